@@ -1,0 +1,184 @@
+// C-ABI entry points of libndc_b200.so: validation, dispatch, status codes.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "ndc_b200.h"
+#include "ndc_common.cuh"
+#include "ndc_generic.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+    return fail(NDC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+constexpr int kMaxChannels = 16;  // per-group channel counts the kernels are sized for
+constexpr int kMaxTaps = 343;
+
+int validate(const NdcDesc* d) {
+    if (!d) return fail(NDC_ERR_INVALID, "descriptor is NULL");
+    if (d->flags & ~NDC_FLAG_FORCE_GENERIC)
+        return fail(NDC_ERR_INVALID, "descriptor.flags has unknown bits set (0x%x)", d->flags);
+    if (d->batch <= 0 || d->groups <= 0 || d->m <= 0 || d->sc <= 0)
+        return fail(NDC_ERR_INVALID, "batch, groups, m and sc must be positive (got %d, %d, %d, %d)",
+                    d->batch, d->groups, d->m, d->sc);
+    if (d->D <= 0 || d->H <= 0 || d->W <= 0)
+        return fail(NDC_ERR_INVALID, "spatial extents must be positive (got %d x %d x %d)", d->D,
+                    d->H, d->W);
+    if (d->kD <= 0 || d->kH <= 0 || d->kW <= 0 || !(d->kD & 1) || !(d->kH & 1) || !(d->kW & 1))
+        return fail(NDC_ERR_INVALID, "kernel extents must be positive and odd (got %d x %d x %d)",
+                    d->kD, d->kH, d->kW);
+    if (d->dtype != NDC_F32 && d->dtype != NDC_BF16)
+        return fail(NDC_ERR_INVALID, "dtype must be NDC_F32 or NDC_BF16 (got %d)", d->dtype);
+    if (!(d->eps >= 0.0f)) return fail(NDC_ERR_INVALID, "eps must be non-negative");
+    if (d->m > kMaxChannels || d->sc > kMaxChannels)
+        return fail(NDC_ERR_UNSUPPORTED, "m and sc are limited to %d per group (got %d, %d)",
+                    kMaxChannels, d->m, d->sc);
+    if ((long long)d->kD * d->kH * d->kW > kMaxTaps)
+        return fail(NDC_ERR_UNSUPPORTED, "kernels are limited to %d taps", kMaxTaps);
+    return NDC_OK;
+}
+
+int check_ptr(const void* p, const char* name, int dtype) {
+    if (!p) return fail(NDC_ERR_INVALID, "%s is NULL", name);
+    const uintptr_t a = (uintptr_t)p;
+    const uintptr_t need = dtype == NDC_BF16 ? 2 : 4;
+    if (a % need) return fail(NDC_ERR_ALIGNMENT, "%s is not aligned to %d bytes", name, (int)need);
+    return NDC_OK;
+}
+
+#define NDC_TRY(expr)                  \
+    do {                               \
+        int _st = (expr);              \
+        if (_st != NDC_OK) return _st; \
+    } while (0)
+
+int path_of(const NdcDesc* d) {
+    (void)d;
+    return NDC_PATH_GENERIC;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ndc_version(void) { return NDC_B200_VERSION; }
+
+const char* ndc_last_error(void) { return g_err; }
+
+const char* ndc_status_string(int status) {
+    switch (status) {
+        case NDC_OK: return "ok";
+        case NDC_ERR_INVALID: return "invalid argument";
+        case NDC_ERR_UNSUPPORTED: return "unsupported geometry";
+        case NDC_ERR_WORKSPACE: return "workspace missing, too small or misaligned";
+        case NDC_ERR_CUDA: return "CUDA error";
+        case NDC_ERR_ALIGNMENT: return "misaligned pointer";
+        default: return "unknown status";
+    }
+}
+
+int ndc_query(const NdcDesc* desc, int32_t* path) {
+    NDC_TRY(validate(desc));
+    if (path) *path = path_of(desc);
+    return NDC_OK;
+}
+
+int ndc_fwd(const NdcDesc* desc, const void* x, const void* z, const float* h, const float* bias,
+            void* out, void* t1, void* stream) {
+    NDC_TRY(validate(desc));
+    NDC_TRY(check_ptr(x, "x", desc->dtype));
+    NDC_TRY(check_ptr(z, "z", desc->dtype));
+    NDC_TRY(check_ptr(h, "h", NDC_F32));
+    NDC_TRY(check_ptr(out, "out", desc->dtype));
+    NDC_TRY(check_ptr(t1, "t1", desc->dtype));
+    if (bias) NDC_TRY(check_ptr(bias, "bias", NDC_F32));
+    const ndc::Geo g = ndc::make_geo(*desc, bias != nullptr);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (desc->dtype == NDC_F32)
+        e = ndc::generic::forward<float>(g, (const float*)x, (const float*)z, h, bias, (float*)out,
+                                         (float*)t1, st);
+    else
+        e = ndc::generic::forward<__nv_bfloat16>(g, (const __nv_bfloat16*)x,
+                                                 (const __nv_bfloat16*)z, h, bias,
+                                                 (__nv_bfloat16*)out, (__nv_bfloat16*)t1, st);
+    if (e != cudaSuccess) return cuda_fail(e, "ndc_fwd launch");
+    return NDC_OK;
+}
+
+size_t ndc_bwd_workspace_bytes(const NdcDesc* desc) {
+    if (validate(desc) != NDC_OK) return 0;
+    const ndc::Geo g = ndc::make_geo(*desc, false);
+    return ndc::generic::bwd_scratch(g).bytes;
+}
+
+int ndc_bwd(const NdcDesc* desc, const void* x, const void* z, const void* t1, const float* h,
+            const float* bias, const void* gout, void* gx, void* gz, float* gh, float* gb,
+            void* workspace, size_t workspace_bytes, void* stream) {
+    NDC_TRY(validate(desc));
+    NDC_TRY(check_ptr(x, "x", desc->dtype));
+    NDC_TRY(check_ptr(z, "z", desc->dtype));
+    NDC_TRY(check_ptr(t1, "t1", desc->dtype));
+    NDC_TRY(check_ptr(h, "h", NDC_F32));
+    NDC_TRY(check_ptr(gout, "gout", desc->dtype));
+    if (bias) NDC_TRY(check_ptr(bias, "bias", NDC_F32));
+    if (gx) NDC_TRY(check_ptr(gx, "gx", desc->dtype));
+    if (gz) NDC_TRY(check_ptr(gz, "gz", desc->dtype));
+    if (gh) NDC_TRY(check_ptr(gh, "gh", NDC_F32));
+    if (gb) NDC_TRY(check_ptr(gb, "gb", NDC_F32));
+    if (gb && !gz) return fail(NDC_ERR_INVALID, "gb needs gz: pass a gz buffer when gb is wanted");
+    if (!gx && !gz && !gh) return NDC_OK;  // nothing wanted
+    const size_t need = ndc_bwd_workspace_bytes(desc);
+    if (!workspace || workspace_bytes < need)
+        return fail(NDC_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need,
+                    workspace ? workspace_bytes : (size_t)0);
+    if ((uintptr_t)workspace % 256)
+        return fail(NDC_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    const ndc::Geo g = ndc::make_geo(*desc, bias != nullptr);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (desc->dtype == NDC_F32)
+        e = ndc::generic::backward<float>(g, (const float*)x, (const float*)z, (const float*)t1, h,
+                                          bias, (const float*)gout, (float*)gx, (float*)gz, gh, gb,
+                                          workspace, st);
+    else
+        e = ndc::generic::backward<__nv_bfloat16>(
+            g, (const __nv_bfloat16*)x, (const __nv_bfloat16*)z, (const __nv_bfloat16*)t1, h, bias,
+            (const __nv_bfloat16*)gout, (__nv_bfloat16*)gx, (__nv_bfloat16*)gz, gh, gb, workspace,
+            st);
+    if (e != cudaSuccess) return cuda_fail(e, "ndc_bwd launch");
+    return NDC_OK;
+}
+
+int ndc_gconv(const NdcDesc* desc, const void* in, const float* h, const float* bias,
+              int32_t adjoint, void* out, void* stream) {
+    NDC_TRY(validate(desc));
+    NDC_TRY(check_ptr(in, "in", desc->dtype));
+    NDC_TRY(check_ptr(h, "h", NDC_F32));
+    NDC_TRY(check_ptr(out, "out", desc->dtype));
+    if (bias) NDC_TRY(check_ptr(bias, "bias", NDC_F32));
+    const ndc::Geo g = ndc::make_geo(*desc, bias != nullptr);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (desc->dtype == NDC_F32)
+        e = ndc::generic::gconv<float>(g, (const float*)in, h, bias, adjoint != 0, (float*)out, st);
+    else
+        e = ndc::generic::gconv<__nv_bfloat16>(g, (const __nv_bfloat16*)in, h, bias, adjoint != 0,
+                                               (__nv_bfloat16*)out, st);
+    if (e != cudaSuccess) return cuda_fail(e, "ndc_gconv launch");
+    return NDC_OK;
+}
+
+}  // extern "C"

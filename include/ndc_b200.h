@@ -1,0 +1,145 @@
+/*
+ * ndc_b200 - nonnegative-deconvolution (NDC) source update for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of the shared library `libndc_b200.so`.  Every entry point takes raw DEVICE pointers,
+ * caller-allocated outputs and workspace, and an explicit CUDA stream; it returns a status
+ * code, never throws and never aborts the process.  Nothing here depends on PyTorch.
+ *
+ * The update (per group g, with m = C/groups filter channels, sc source channels,
+ * pad = k/2, all convolutions stride 1, zero padded, odd kernels):
+ *
+ *     K(u)[o,p] = sum_{i,tau} u[i, p + tau - pad] * h[o,i,tau]
+ *     A(v)[i,p] = sum_{o,tau} v[o, p + pad - tau] * h[o,i,tau]          (A = K^T)
+ *     s   = relu(z + bias)            (ReLU and bias optional, see NdcDesc)
+ *     t1  = K(s)
+ *     out = (s * (A(x) + eps)) / (A(t1) + eps)
+ *
+ * Tensor layout: contiguous, channels first.
+ *     x, t1, gx            (batch, groups*m,  D, H, W)
+ *     z, out, gout, gz     (batch, groups*sc, D, H, W)
+ *     h, gh                (groups*m, sc, kD, kH, kW)      always float32
+ *     bias, gb             (groups*sc)                     always float32
+ * 1-D and 2-D problems set the leading extents (and kernel extents) to 1.
+ * The large tensors are stored as float32 or bfloat16 (NdcDesc.dtype); all arithmetic and
+ * every reduction is float32.
+ *
+ * Each declaration cites the interface of the reference project (pashtari/deconver, paths
+ * within that project) that it replaces.
+ */
+#ifndef NDC_B200_H
+#define NDC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NDC_B200_VERSION 1
+
+enum NdcDType { NDC_F32 = 0, NDC_BF16 = 1 };
+
+enum NdcStatus {
+    NDC_OK = 0,
+    NDC_ERR_INVALID = 1,     /* null pointer, non-positive extent, even kernel, bad dtype   */
+    NDC_ERR_UNSUPPORTED = 2, /* geometry outside what the kernels cover                     */
+    NDC_ERR_WORKSPACE = 3,   /* workspace missing, too small or misaligned                  */
+    NDC_ERR_CUDA = 4,        /* a CUDA runtime call or a launch failed                      */
+    NDC_ERR_ALIGNMENT = 5    /* a tensor pointer is not aligned to its element size         */
+};
+
+enum NdcFlags {
+    NDC_FLAG_FORCE_GENERIC = 1 /* run the generic kernels even where the tiled ones apply    */
+};
+
+/* Which family of kernels a geometry runs on (informational; results are the same). */
+enum NdcPath {
+    NDC_PATH_GENERIC = 0, /* any m, sc <= 16, any odd kernel with <= 343 taps                */
+    NDC_PATH_DEPTHWISE4 = 1 /* m = 1, sc = 4, kernel 3x3x3, 1x5x5 or 1x3x3: tiled, fused     */
+};
+
+/*
+ * Geometry of one update.  Mirrors the arguments of the reference's
+ * `DeconvUpdate.forward(ctx, x, z, h, bias, groups, m, sc, eps, relu_input)`
+ * (deconver/deconvolution/functional.py:105-106) plus the launch geometry its wrappers
+ * derive from the tensors (deconver/deconvolution/kernels.py:687-725).
+ */
+typedef struct NdcDesc {
+    int32_t batch;
+    int32_t groups;
+    int32_t m;          /* filter (input) channels per group                               */
+    int32_t sc;         /* source channels per group                                       */
+    int32_t D, H, W;    /* spatial extent; missing leading dimensions are 1                */
+    int32_t kD, kH, kW; /* kernel extent, all odd; missing leading dimensions are 1        */
+    float eps;          /* added to numerator and denominator                              */
+    int32_t relu_input; /* 1: s = relu(z + bias) (first iteration); 0: s = z + bias        */
+    int32_t dtype;      /* NdcDType of x, z, t1, out, gout, gx, gz                         */
+    int32_t flags;      /* bitwise OR of NdcFlags; 0 for normal use                        */
+} NdcDesc;
+
+/* Library version (NDC_B200_VERSION of the build). */
+int ndc_version(void);
+
+/* Message of the last failure on the calling thread ("" if none).  Replaces the Python
+ * exceptions of the reference's wrappers (deconver/deconvolution/kernels.py:715-716). */
+const char *ndc_last_error(void);
+
+/* Short name of a status code. */
+const char *ndc_status_string(int status);
+
+/*
+ * Whether a geometry is covered, and by which kernel family.  Returns NDC_OK and writes an
+ * NdcPath to *path, or NDC_ERR_INVALID / NDC_ERR_UNSUPPORTED.  Host-only; no CUDA call.
+ * Replaces `kernels_supported` / `wgrad_supported` / `triton_available`
+ * (deconver/deconvolution/kernels.py:114-163).
+ */
+int ndc_query(const NdcDesc *desc, int32_t *path);
+
+/*
+ * Forward of one update: writes `out` and `t1` (t1 is what backward needs, besides x and z).
+ * `bias` may be NULL.  Replaces `kernels.gconv` + `kernels.deconv_fwd` as called by
+ * `DeconvUpdate.forward` (deconver/deconvolution/functional.py:105-116;
+ * deconver/deconvolution/kernels.py:728-788).
+ */
+int ndc_fwd(const NdcDesc *desc, const void *x, const void *z, const float *h,
+            const float *bias, void *out, void *t1, void *stream);
+
+/*
+ * Bytes of scratch `ndc_bwd` needs for this geometry (0 on an invalid descriptor).  The
+ * workspace must be 256-byte aligned device memory; its contents need not be initialised
+ * and are undefined afterwards.
+ */
+size_t ndc_bwd_workspace_bytes(const NdcDesc *desc);
+
+/*
+ * Backward of one update.  Inputs: x, z, t1 (as written by ndc_fwd), h, bias (or NULL),
+ * upstream gradient gout.  Outputs, each optional (NULL = not wanted):
+ *     gx  gradient w.r.t. x
+ *     gz  gradient w.r.t. z           (required if gb is wanted)
+ *     gh  gradient w.r.t. h, float32, overwritten (not accumulated into)
+ *     gb  gradient w.r.t. bias, float32, overwritten
+ * The reductions behind gh and gb use a fixed partition and a fixed summation order:
+ * results are bitwise reproducible from run to run.
+ * Replaces the seven kernel launches and four torch reductions of `DeconvUpdate.backward`
+ * (deconver/deconvolution/functional.py:118-182; kernels `deconv_bwd`, `gconv`, `wgrad`,
+ * `deconv_gz`, deconver/deconvolution/kernels.py:791-894).
+ */
+int ndc_bwd(const NdcDesc *desc, const void *x, const void *z, const void *t1, const float *h,
+            const float *bias, const void *gout, void *gx, void *gz, float *gh, float *gb,
+            void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Grouped convolution K (adjoint = 0: groups*sc -> groups*m channels) or its adjoint A
+ * (adjoint = 1: groups*m -> groups*sc channels) of a tensor of dtype desc->dtype.
+ * With adjoint = 0, `bias` (or NULL) and desc->relu_input are applied to the input as it is
+ * read, and out-of-volume taps contribute 0.  Replaces `kernels.gconv`
+ * (deconver/deconvolution/kernels.py:728-759).
+ */
+int ndc_gconv(const NdcDesc *desc, const void *in, const float *h, const float *bias,
+              int32_t adjoint, void *out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NDC_B200_H */

@@ -1,0 +1,95 @@
+"""The C-ABI library loads without a GPU and exports every symbol the header declares.
+No compute call is made here; only host-side queries."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+from deconver_b200 import _lib
+from deconver_b200._build import build_library
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build_library()
+    return _lib.load()
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "ndc_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ndc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_and_binding_agree(lib):
+    declared = _declared_functions()
+    assert declared, "no declarations parsed from the header"
+    assert sorted(_lib.SYMBOLS) == declared
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared but not exported"
+
+
+def test_descriptor_layout():
+    # 10 int32 + float + 3 int32, no padding: the struct the header declares
+    assert ctypes.sizeof(_lib.NdcDesc) == 56
+    assert _lib.NdcDesc.eps.offset == 40 and _lib.NdcDesc.flags.offset == 52
+
+
+def test_version_and_status_strings(lib):
+    assert lib.ndc_version() == 1
+    assert lib.ndc_status_string(0) == b"ok"
+    for code in range(1, 6):
+        assert lib.ndc_status_string(code) not in (b"ok", b"unknown status")
+    assert lib.ndc_status_string(99) == b"unknown status"
+
+
+def _desc(**kw):
+    base = dict(batch=2, groups=8, m=1, sc=4, spatial=(6, 5, 7), kernel_size=(3, 3, 3),
+                eps=1e-16, relu_input=True, dtype_code=_lib.NDC_F32)
+    base.update(kw)
+    return _lib.make_desc(**base)
+
+
+def test_query_accepts_and_rejects(lib):
+    path = ctypes.c_int32(-1)
+    assert lib.ndc_query(_desc(), ctypes.byref(path)) == 0
+    assert path.value in (_lib.PATH_GENERIC, _lib.PATH_DEPTHWISE4)
+    assert lib.ndc_query(_desc(flags=_lib.FLAG_FORCE_GENERIC), ctypes.byref(path)) == 0
+    assert path.value == _lib.PATH_GENERIC
+    assert lib.ndc_query(_desc(kernel_size=(3, 4, 3)), None) == 1  # even kernel
+    assert b"odd" in lib.ndc_last_error()
+    assert lib.ndc_query(_desc(batch=0), None) == 1
+    assert lib.ndc_query(_desc(dtype_code=7), None) == 1
+    assert lib.ndc_query(_desc(flags=64), None) == 1
+    assert lib.ndc_query(_desc(m=17), None) == 2  # beyond the kernels' channel limit
+    assert lib.ndc_query(None, None) == 1
+
+
+def test_workspace_query(lib):
+    assert lib.ndc_bwd_workspace_bytes(_desc()) > 0
+    assert lib.ndc_bwd_workspace_bytes(_desc(kernel_size=(2, 3, 3))) == 0
+    big = lib.ndc_bwd_workspace_bytes(_desc(batch=32, groups=64, spatial=(128, 128, 128)))
+    assert big > 0  # 64-bit size arithmetic: no overflow on >2^31-element tensors
+
+
+def test_null_pointers_are_refused_without_touching_the_gpu(lib):
+    d = _desc()
+    assert lib.ndc_fwd(d, None, None, None, None, None, None, None) == 1
+    assert b"NULL" in lib.ndc_last_error()
+    assert lib.ndc_bwd(d, None, None, None, None, None, None, None, None, None, None, None, 0,
+                       None) == 1
+    assert lib.ndc_gconv(d, None, None, None, 0, None, None) == 1
+
+
+def test_rank_padding():
+    d = _lib.make_desc(1, 4, 1, 4, (11,), (5,), 1e-16, True, 0)
+    assert (d.D, d.H, d.W, d.kD, d.kH, d.kW) == (1, 1, 11, 1, 1, 5)
+    d = _lib.make_desc(1, 4, 1, 4, (9, 8), (3, 5), 1e-16, False, 1)
+    assert (d.D, d.H, d.W, d.kD, d.kH, d.kW) == (1, 9, 8, 1, 3, 5)
+    with pytest.raises(ValueError):
+        _lib.make_desc(1, 4, 1, 4, (2, 2, 2, 2), (3, 3, 3, 3), 0.0, True, 0)
+    with pytest.raises(ValueError):
+        _lib.make_desc(1, 4, 1, 4, (9, 8), (3,), 0.0, True, 0)

@@ -1,0 +1,283 @@
+"""Parity of the CUDA path with the reference, through the C ABI, on a GPU.
+
+* against the golden fixtures produced by the reference's own `ReferenceDeconv`;
+* against the CPU oracle on seeded inputs at sizes it finishes in seconds;
+* the cases the reference's `tests/test_deconv_equivalence.py` covers: stage geometries,
+  grouping / kernel / rank variations, batch sizes, several iterations, partial gradient
+  requests, non-contiguous input, double backward refused.
+
+Tolerances (max-norm relative error, `max|a-b| / max|b|`, the reference's own metric):
+float32: 1e-4 for one update (forward and every gradient), 1e-3 after several iterations;
+bfloat16 storage with float32 accumulation: 2e-2 against the float32 oracle.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+import deconver_b200 as dcb
+from conftest import golden_names, load_golden, max_norm_error, update_cfg
+from deconver_b200 import functional as Fn
+from oracle import ndc_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-4
+F32_ITER_TOL = 1e-3
+BF16_TOL = 2e-2
+
+UPDATE = golden_names("update_")
+LAYER = golden_names("layer_")
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    dcb.load_library()  # fails loudly if the CUDA library is missing
+    return torch.device("cuda:0")
+
+
+def _cuda(a, dev, dtype=torch.float32, grad=True):
+    if a is None:
+        return None
+    t = torch.from_numpy(np.asarray(a)).to(device=dev, dtype=dtype)
+    return t.requires_grad_(grad)
+
+
+def _run_update(g, dev, dtype, generic=False):
+    cfg = update_cfg(g)
+    x, z, h, b = (_cuda(g.get(k), dev, dtype if k in ("x", "z") else torch.float32)
+                  for k in ("x", "z", "h", "bias"))
+    with Fn.force_generic(generic):
+        out = dcb.deconv_update(x, z, h, b, **cfg)
+        out.backward(_cuda(g["gout"], dev, dtype, grad=False))
+    torch.cuda.synchronize()
+    return dict(out=out.detach(), gx=x.grad, gz=z.grad, gh=h.grad,
+                gb=None if b is None else b.grad)
+
+
+@pytest.mark.parametrize("generic", [False, True], ids=["default", "generic"])
+@pytest.mark.parametrize("name", UPDATE)
+def test_update_matches_reference_fixture_f32(dev, name, generic):
+    g = load_golden(name)
+    got = _run_update(g, dev, torch.float32, generic)
+    for k, v in got.items():
+        if v is None:
+            continue
+        err = max_norm_error(v.float().cpu().numpy(), g[f"{k}_f64"])
+        assert err < F32_TOL, f"{name}: {k} error {err:.3e}"
+
+
+@pytest.mark.parametrize("name", ["update_dw3d", "update_dw2d_k5", "update_grouped",
+                                  "update_dw3d_wide", "update_later_iter"])
+def test_update_bf16_storage(dev, name):
+    """bfloat16 tensors, float32 arithmetic: compared with the float32-precision oracle on the
+    same bfloat16-rounded inputs."""
+    g = load_golden(name)
+    cfg = update_cfg(g)
+    rounded = {k: torch.from_numpy(g[k]).to(torch.bfloat16).double() for k in ("x", "z", "gout")}
+    ref = O.deconv_update_grads(
+        rounded["x"], rounded["z"], torch.from_numpy(g["h"]).double(),
+        None if "bias" not in g else torch.from_numpy(g["bias"]).double(), rounded["gout"], **cfg)
+    got = _run_update(g, dev, torch.bfloat16)
+    for k, r in zip(("out", "gx", "gz", "gh", "gb"), ref):
+        if r is None:
+            continue
+        err = max_norm_error(got[k].float().cpu().numpy(), r.numpy())
+        assert err < BF16_TOL, f"{name}: {k} error {err:.3e}"
+    assert got["out"].dtype == torch.bfloat16 and got["gh"].dtype == torch.float32
+
+
+def _layer(g, dev, dtype=torch.float32):
+    ks = tuple(int(k) for k in g["kernel_size"])
+    C = g["x"].shape[1]
+    mod = dcb.Deconv(C, ks, source_channels=int(g["sc"]), groups=int(g["groups"]),
+                     eps=float(g["eps"]), num_iters=int(g["num_iters"]),
+                     num_grad_iters=int(g["num_grad_iters"]))
+    mod.load_state_dict({
+        "init.h0": torch.from_numpy(g["h0"]),
+        "init.linear.linear.weight": torch.from_numpy(g["weight"]),
+        "init.linear.linear.bias": torch.from_numpy(g["bias"]),
+    })
+    return mod.to(device=dev, dtype=dtype)
+
+
+@pytest.mark.parametrize("name", LAYER)
+def test_layer_matches_reference_fixture(dev, name):
+    """Whole layer (projection + updates).  The projection is a library GEMM; TF32 is turned
+    off so that it is a float32 product as on the CPU."""
+    g = load_golden(name)
+    if name.endswith("nobias_shift"):
+        pytest.skip("ill-conditioned on purpose (den = eps); covered at the update boundary")
+    old = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        mod = _layer(g, dev)
+        x = _cuda(g["x"], dev)
+        y = mod(x)
+        y.backward(_cuda(g["gout"], dev, grad=False))
+        torch.cuda.synchronize()
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old
+    iters = int(g["num_iters"])
+    tol = F32_TOL if iters == 1 else F32_ITER_TOL
+    assert max_norm_error(y.detach().cpu().numpy(), g["y_f64"]) < tol
+    grads = {"gx": x.grad, "gh0": mod.init.h0.grad, "gweight": mod.init.linear.linear.weight.grad,
+             "gbias": mod.init.linear.linear.bias.grad}
+    gtol = 1e-3 if iters == 1 else 5e-3  # the reference's own gradient tolerances
+    for k, v in grads.items():
+        ref = g.get(f"{k}_f64")
+        if ref is None:
+            assert v is None, f"{name}: {k} should have no gradient"
+            continue
+        assert max_norm_error(v.cpu().numpy(), ref) < gtol, (name, k)
+
+
+RANDOM_CASES = [
+    # C, groups, sc, kernel, batch, spatial
+    (32, 32, 4, (3, 3, 3), 2, (12, 14, 13)),   # reference stage geometries
+    (64, 64, 4, (3, 3, 3), 2, (10, 9, 11)),
+    (128, 128, 4, (3, 3, 3), 2, (8, 8, 8)),
+    (256, 256, 4, (3, 3, 3), 2, (6, 5, 4)),
+    (8, 8, 4, (3, 3, 3), 1, (20, 33, 70)),     # wider than one tile in every direction
+    (4, 4, 4, (3, 3, 3), 1, (3, 40, 130)),
+    (6, 6, 4, (5, 5), 2, (70, 150)),
+    (6, 6, 4, (3, 3), 2, (37, 41)),
+    (4, 4, 4, (3, 3, 3), 2, (1, 1, 1)),        # degenerate extents
+    (4, 4, 4, (3, 3, 3), 1, (2, 1, 5)),
+    (4, 4, 4, (5, 5), 1, (1, 3)),
+    (6, 2, 5, (3, 3, 3), 2, (5, 6, 7)),        # m = 3, sc = 5
+    (4, 4, 2, (7,), 2, (40,)),
+]
+
+
+@pytest.mark.parametrize("case", RANDOM_CASES, ids=lambda c: "C%d_g%d_sc%d_k%s_b%d_%s" % (
+    c[0], c[1], c[2], "x".join(map(str, c[3])), c[4], "x".join(map(str, c[5]))))
+@pytest.mark.parametrize("relu_input", [True, False])
+def test_update_matches_oracle_on_seeded_inputs(dev, case, relu_input):
+    C, G, sc, ks, B, spatial = case
+    m = C // G
+    gen = torch.Generator().manual_seed(1234 + C + len(spatial))
+    x = torch.rand(B, C, *spatial, generator=gen)
+    z = torch.randn(B, G * sc, *spatial, generator=gen) * 0.5 + 0.3
+    if not relu_input:
+        z = z.abs()
+    h = torch.rand(C, sc, *ks, generator=gen) / float(np.prod(ks))
+    bias = torch.randn(G * sc, generator=gen) * 0.1 if relu_input else None
+    gout = torch.randn(B, G * sc, *spatial, generator=gen)
+    cfg = dict(groups=G, m=m, sc=sc, eps=1e-16, relu_input=relu_input)
+    ref = O.deconv_update_grads(x.double(), z.double(), h.double(),
+                                None if bias is None else bias.double(), gout.double(), **cfg)
+    xd, zd, hd = (t.to(dev).requires_grad_(True) for t in (x, z, h))
+    bd = None if bias is None else bias.to(dev).requires_grad_(True)
+    out = dcb.deconv_update(xd, zd, hd, bd, **cfg)
+    out.backward(gout.to(dev))
+    torch.cuda.synchronize()
+    got = (out.detach(), xd.grad, zd.grad, hd.grad, None if bd is None else bd.grad)
+    for k, a, r in zip(("out", "gx", "gz", "gh", "gb"), got, ref):
+        if r is None:
+            continue
+        err = max_norm_error(a.cpu().numpy(), r.numpy())
+        assert err < F32_TOL, f"{k} error {err:.3e}"
+
+
+def test_partial_gradient_requests(dev):
+    """Every subset of {x, z, h, bias}.requires_grad gives the same values as the full run
+    (reference: tests/test_deconv_equivalence.py:211-242)."""
+    g = load_golden("update_dw3d")
+    cfg = update_cfg(g)
+    full = _run_update(g, dev, torch.float32)
+    names = ("x", "z", "h", "bias")
+    keys = dict(x="gx", z="gz", h="gh", bias="gb")
+    for mask in range(16):
+        t = {k: _cuda(g[k], dev, grad=bool(mask >> i & 1)) for i, k in enumerate(names)}
+        out = dcb.deconv_update(t["x"], t["z"], t["h"], t["bias"], **cfg)
+        assert torch.equal(out.detach(), full["out"])
+        if mask == 0:
+            assert not out.requires_grad
+            continue
+        out.backward(_cuda(g["gout"], dev, grad=False))
+        for i, k in enumerate(names):
+            if mask >> i & 1:
+                assert torch.equal(t[k].grad, full[keys[k]]), (mask, k)
+            else:
+                assert t[k].grad is None
+
+
+def test_results_are_bitwise_reproducible(dev):
+    g = load_golden("update_b3")
+    a = _run_update(g, dev, torch.float32)
+    b = _run_update(g, dev, torch.float32)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+
+
+def test_non_contiguous_input(dev):
+    g = load_golden("layer_dw3d")
+    mod = _layer(g, dev)
+    base = torch.rand(2, 16, 7, 6, 16, device=dev)
+    x = base[..., ::2]
+    assert not x.is_contiguous()
+    with torch.no_grad():
+        assert torch.equal(mod(x), mod(x.contiguous()))
+
+
+def test_double_backward_is_refused(dev):
+    g = load_golden("update_dw3d")
+    cfg = update_cfg(g)
+    x, z, h, b = (_cuda(g[k], dev) for k in ("x", "z", "h", "bias"))
+    out = dcb.deconv_update(x, z, h, b, **cfg)
+    with pytest.raises(RuntimeError, match="double backward"):
+        torch.autograd.grad(out.sum(), x, create_graph=True)
+
+
+def test_fit_returns_batched_filter(dev):
+    g = load_golden("layer_grouped")
+    mod = _layer(g, dev)
+    x = _cuda(g["x"], dev, grad=False)
+    with torch.no_grad():
+        s, h = mod.fit(x)
+        assert h.shape == (x.shape[0], *mod.init.h0.shape) and h.is_contiguous()
+        assert torch.equal(h[0], torch.relu(mod.init.h0)) and torch.equal(s, mod(x))
+        x_hat = mod.reconstruct(s, h)
+    assert x_hat.shape == x.shape
+
+
+def test_gconv_adjoint_identity(dev):
+    """<K u, v> = <u, A v>: a size-independent property of the two operators."""
+    torch.manual_seed(3)
+    G, m, sc, ks = 16, 1, 4, (3, 3, 3)
+    u = torch.randn(2, G * sc, 24, 20, 36, device=dev)
+    v = torch.randn(2, G * m, 24, 20, 36, device=dev)
+    h = torch.rand(G * m, sc, *ks, device=dev)
+    ku = dcb.gconv(u, h, groups=G, m=m, sc=sc, adjoint=False)
+    av = dcb.gconv(v, h, groups=G, m=m, sc=sc, adjoint=True)
+    lhs = (ku.double() * v.double()).sum().item()
+    rhs = (u.double() * av.double()).sum().item()
+    assert abs(lhs - rhs) < 1e-5 * max(abs(lhs), 1.0)
+
+
+def test_abi_status_codes_on_device(dev):
+    """Direct C-ABI calls with raw pointers: a short workspace is refused with a status."""
+    from deconver_b200 import _lib
+    lib = _lib.load()
+    d = _lib.make_desc(1, 4, 1, 4, (4, 4, 4), (3, 3, 3), 1e-16, True, _lib.NDC_F32)
+    x = torch.rand(1, 4, 4, 4, 4, device=dev)
+    z = torch.rand(1, 16, 4, 4, 4, device=dev)
+    h = torch.rand(4, 4, 3, 3, 3, device=dev)
+    out, t1 = torch.empty_like(z), torch.empty_like(x)
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.ndc_fwd(d, x.data_ptr(), z.data_ptr(), h.data_ptr(), None, out.data_ptr(),
+                       t1.data_ptr(), st) == 0
+    gx = torch.empty_like(x)
+    need = lib.ndc_bwd_workspace_bytes(d)
+    ws = torch.empty(need, dtype=torch.uint8, device=dev)
+    args = (d, x.data_ptr(), z.data_ptr(), t1.data_ptr(), h.data_ptr(), None, z.data_ptr(),
+            gx.data_ptr(), None, None, None)
+    assert lib.ndc_bwd(*args, ws.data_ptr(), max(need - 1, 0), st) == 3
+    assert lib.ndc_bwd(*args, None, need, st) == 3
+    assert lib.ndc_bwd(*args, ws.data_ptr(), need, st) == 0
+    assert lib.ndc_fwd(d, x.data_ptr() + 1, z.data_ptr(), h.data_ptr(), None, out.data_ptr(),
+                       t1.data_ptr(), st) == 5
+    torch.cuda.synchronize()
