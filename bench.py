@@ -1,0 +1,374 @@
+"""Benchmark of the NDC mixer layer (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One JSON line is printed by rank 0.  A "step" is one forward + backward of a single 3-D NDC
+layer on one batch of synthetic input resident in HBM:
+
+    NDC(channels=64, ratio=4, groups=-1, kernel_size=(3,3,3)), fp32,
+    X = rand(2, 64, 64, 64, 64), h0 = |randn|/27, upstream gradient randn(2, 256, 64, 64, 64)
+
+`value` is voxels/s (one voxel = one spatial site of one sample), aggregated over all ranks.
+With N > 1 every rank works on its own batch of 2 (weak scaling, batch sharding) and the
+parameter gradients (dK, projection weight and bias) are averaged with one NCCL all-reduce
+inside the step.  `e2e` is the same step through the public `Deconv` module with pinned HOST
+input and upstream gradient, host<->device copies inside the timed region.
+`--impl reference` times the reference algorithm's PyTorch CPU path (the oracle port) on the
+host cores instead.
+"""
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch
+
+METRIC = "ndc_mixer_fwd_bwd_voxels_per_sec"
+UNIT = "voxels/s"
+WORKLOAD = dict(channels=64, ratio=4, kernel_size=(3, 3, 3), batch=2, spatial=(64, 64, 64))
+WORKLOAD_NAME = ("single 3D NDC mixer layer fwd+bwd (dX, dK), fp32, X (2,64,64,64,64), "
+                 "source 256 ch, K (256,1,3,3,3)")
+# measured on this pool's B200 with an FFMA-only kernel (profiles/fp32_fma_peak.md)
+FP32_FMA_PEAK_TFLOPS = 72.6
+# DRAM bytes per ndc_bwd call from an ncu capture, or None until one has been taken
+# (profiles/ names the capture); scaled to the bench workload by voxel count
+BWD_DRAM_TRAFFIC_BYTES = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons (read-only NVML queries) while a region runs."""
+
+    REASONS = {
+        0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap",
+        0x8: "hw_slowdown", 0x10: "sync_boost", 0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting",
+    }
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _loop(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                bits = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if bits & bit and name != "gpu_idle":
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ------------------------------------------------------------------------- CPU baseline
+
+
+def cpu_layer_step(batch, spatial, threads, seed=0):
+    """One forward+backward of the layer on the CPU with the oracle's PyTorch port of the
+    reference's eager path.  Returns seconds."""
+    from oracle import ndc_oracle
+
+    torch.set_num_threads(threads)
+    C, r, ks = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"]
+    gen = torch.Generator().manual_seed(seed)
+    x = torch.rand(batch, C, *spatial, generator=gen).requires_grad_(True)
+    w = (torch.randn(C * r, C, 1, generator=gen) / C ** 0.5).requires_grad_(True)
+    b = torch.zeros(C * r).requires_grad_(True)
+    h0 = (torch.randn(C, r, *ks, generator=gen).abs() / 27).requires_grad_(True)
+    g = torch.randn(batch, C * r, *spatial, generator=gen)
+    t0 = time.perf_counter()
+    y = ndc_oracle.ndc_layer(x, w, b, h0, groups=C)
+    y.backward(g)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(budget_s=25.0):
+    """Bounded CPU sample: the workload's volume cut to a depth slab so it fits the budget."""
+    threads = os.cpu_count() or 1
+    cpu_layer_step(1, (4, 16, 16), threads)  # thread-pool warm-up
+    probe_shape = (8, 64, 64)
+    t_probe = cpu_layer_step(1, probe_shape, threads)
+    per_voxel = t_probe / (8 * 64 * 64)
+    depth = int(max(8, min(64, budget_s / (per_voxel * 64 * 64))))
+    batch = 2 if per_voxel * 2 * 64 ** 3 <= budget_s else 1
+    if batch == 2:
+        depth = 64
+    spatial = (depth, 64, 64)
+    t = cpu_layer_step(batch, spatial, threads)
+    vox = batch * depth * 64 * 64
+    return {
+        "value": vox / t, "unit": UNIT, "cores": threads, "kind": "port",
+        "sample": f"1 fwd+bwd of the layer on X ({batch},64,{depth},64,64), fp32, "
+                  f"torch {torch.__version__} CPU, {t:.2f} s",
+    }
+
+
+def run_reference(args):
+    """`--impl reference`: the reference algorithm's CPU path, timed on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    cpu_layer_step(1, (4, 16, 16), threads)
+    t_probe = cpu_layer_step(1, (8, 64, 64), threads)
+    per_voxel = t_probe / (8 * 64 * 64)
+    total_steps = args.steps + args.warmup
+    budget = 150.0 / max(total_steps, 1)
+    depth = int(max(4, min(64, budget / (per_voxel * 64 * 64))))
+    spatial = (depth, 64, 64)
+    for _ in range(args.warmup):
+        cpu_layer_step(1, spatial, threads)
+    times = [cpu_layer_step(1, spatial, threads) for _ in range(args.steps)]
+    total = sum(times)
+    vox = depth * 64 * 64
+    value = vox * args.steps / total
+    sample = (f"{args.steps} fwd+bwd steps of the layer on X (1,64,{depth},64,64) "
+              f"(depth slab of the workload), fp32, PyTorch CPU, {threads} threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD_NAME, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- GPU arm
+
+
+def run_b200(args):
+    import torch.distributed as dist
+
+    import deconver_b200 as dcb
+    from deconver_b200 import _lib
+    from deconver_b200 import functional as Fn
+    from deconver_b200.distributed import GradBucket, init_from_env
+
+    rank, world, local = init_from_env("nccl")
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    lib = dcb.load_library()  # raises if the CUDA library is missing
+
+    C, r, ks = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"]
+    B, S = WORKLOAD["batch"], WORKLOAD["spatial"]
+    torch.manual_seed(rank)
+    layer = dcb.NDC(channels=C, ratio=r, groups=-1, kernel_size=ks).to(dev)
+    with torch.no_grad():
+        layer.init.h0.copy_(torch.randn(C, r, *ks, device=dev).abs() / 27)
+    x = torch.rand(B, C, *S, device=dev)
+    gout = torch.randn(B, C * r, *S, device=dev)
+    bucket = GradBucket(layer.parameters())
+    vox_per_step = B * S[0] * S[1] * S[2]
+
+    def step(xin, gin):
+        bucket.zero()
+        xin.grad = None
+        y = layer(xin)
+        y.backward(gin)
+        bucket.allreduce_mean()
+        return y
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    x.requires_grad_(True)
+    for _ in range(max(args.warmup, 3)):
+        step(x, gout)
+    barrier()
+
+    # ---- timed region: K steps, device-resident inputs (each tensor is larger than L2)
+    launches0 = lib.ndc_launch_count()
+    Fn.timing.enable()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            step(x, gout)
+        ev1.record()
+        barrier()
+    ms_total = ev0.elapsed_time(ev1)
+    kernel_ms = Fn.timing.disable_and_collect()
+    launches = lib.ndc_launch_count() - launches0
+    t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    value = world * vox_per_step * args.steps / (ms_total * 1e-3)
+
+    # ---- e2e: pinned host tensors in, results back to pinned host memory, every step
+    x_host = torch.rand(B, C, *S).pin_memory()
+    g_host = torch.randn(B, C * r, *S).pin_memory()
+    y_host = torch.empty(B, C * r, *S).pin_memory()
+    gx_host = torch.empty(B, C, *S).pin_memory()
+    grads_host = torch.empty_like(bucket.flat, device="cpu").pin_memory()
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
+        gd = g_host.to(dev, non_blocking=True)
+        y = step(xd, gd)
+        y_host.copy_(y.detach(), non_blocking=True)
+        gx_host.copy_(xd.grad, non_blocking=True)
+        grads_host.copy_(bucket.flat, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e2e_steps = max(1, min(args.steps, 10))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = world * vox_per_step * e2e_steps / (float(te.item()) * 1e-3)
+    h2d = x_host.numel() * 4 + g_host.numel() * 4
+    d2h = y_host.numel() * 4 + gx_host.numel() * 4 + grads_host.numel() * 4
+
+    if rank != 0:
+        return
+
+    # ---- roofline of the dominant call (ndc_bwd), from live CUDA-event timings
+    peak, peak_kind = load_peaks()
+    e = 4  # bytes per element (fp32 storage)
+    bwd_bytes = 14 * C * e * vox_per_step  # read x, z, gout; write gx, gz (ratio 4)
+    fwd_bytes = 9 * C * e * vox_per_step   # read x, z; write out
+    bwd_ms = statistics.mean(kernel_ms["ndc_bwd"]) if kernel_ms["ndc_bwd"] else None
+    fwd_ms = statistics.mean(kernel_ms["ndc_fwd"]) if kernel_ms["ndc_fwd"] else None
+    taps = ks[0] * ks[1] * ks[2]
+    bwd_flops = 2 * 8 * r * taps * C * vox_per_step
+    fwd_flops = 2 * 3 * r * taps * C * vox_per_step
+    achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9 if bwd_ms else None
+    roofline = {
+        "bound": "hbm", "kernel": "ndc_bwd (all launches of one backward call)",
+        "achieved": achieved, "peak": peak, "unit": "GB/s",
+        "frac": achieved / peak if achieved else None, "peak_kind": peak_kind,
+        "traffic": BWD_DRAM_TRAFFIC_BYTES,
+        "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
+        "fp32_fma": {
+            "achieved_tflops": bwd_flops / (bwd_ms * 1e-3) / 1e12 if bwd_ms else None,
+            "peak_tflops": FP32_FMA_PEAK_TFLOPS,
+            "frac": bwd_flops / (bwd_ms * 1e-3) / 1e12 / FP32_FMA_PEAK_TFLOPS if bwd_ms else None,
+        },
+        "fwd": {
+            "ms": fwd_ms, "algorithmic_bytes": fwd_bytes,
+            "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9 if fwd_ms else None,
+            "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak if fwd_ms else None,
+            "fp32_fma_frac": fwd_flops / (fwd_ms * 1e-3) / 1e12 / FP32_FMA_PEAK_TFLOPS
+            if fwd_ms else None,
+        },
+        "fwd_bwd_frac": (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak
+        if fwd_ms and bwd_ms else None,
+    }
+
+    path = _lib.load().ndc_query  # which kernel family ran
+    import ctypes
+    pth = ctypes.c_int32(-1)
+    path(_lib.make_desc(B, C, 1, r, S, ks, 1e-16, True, _lib.NDC_F32), ctypes.byref(pth))
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {
+            "workload": WORKLOAD_NAME, "per_gpu_batch": B, "global_batch": B * world,
+            "parallelism": f"batch-sharded x{world}" + (", NCCL grad all-reduce" if world > 1 else ""),
+            "l2": "inputs larger than L2 (x 134 MB, z/out/gout 537 MB each vs 126 MB L2)",
+            "kernel_path": {0: "generic", 1: "depthwise4"}.get(pth.value, "?"),
+        },
+        "roofline": roofline,
+        "clocks": clocks.summary(),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": int(launches),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true",
+                    help="skip the CPU-baseline leg (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -16,7 +16,8 @@ FLAG_FORCE_GENERIC = 1
 
 # every symbol `include/ndc_b200.h` declares
 SYMBOLS = (
-    "ndc_version", "ndc_last_error", "ndc_status_string", "ndc_query", "ndc_fwd",
+    "ndc_version", "ndc_last_error", "ndc_status_string", "ndc_launch_count", "ndc_query",
+    "ndc_fwd",
     "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_gconv",
 )
 
@@ -60,6 +61,7 @@ def load():
     lib.ndc_last_error.restype = ctypes.c_char_p
     lib.ndc_status_string.restype = ctypes.c_char_p
     lib.ndc_status_string.argtypes = [ctypes.c_int]
+    lib.ndc_launch_count.restype = ctypes.c_uint64
     lib.ndc_query.restype = ctypes.c_int
     lib.ndc_query.argtypes = [dp, ctypes.POINTER(ctypes.c_int32)]
     lib.ndc_fwd.restype = ctypes.c_int

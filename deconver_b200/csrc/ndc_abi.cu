@@ -89,6 +89,10 @@ const char* ndc_status_string(int status) {
     }
 }
 
+uint64_t ndc_launch_count(void) {
+    return (uint64_t)ndc::launch_counter().load(std::memory_order_relaxed);
+}
+
 int ndc_query(const NdcDesc* desc, int32_t* path) {
     NDC_TRY(validate(desc));
     if (path) *path = path_of(desc);

@@ -7,7 +7,17 @@
 
 #include "ndc_b200.h"
 
+#include <atomic>
+
 namespace ndc {
+
+// Process-wide count of kernel launches, for ndc_launch_count().
+inline std::atomic<unsigned long long>& launch_counter() {
+    static std::atomic<unsigned long long> n{0};
+    return n;
+}
+// Call once after every kernel launch.
+inline void launched(int n = 1) { launch_counter().fetch_add(n, std::memory_order_relaxed); }
 
 // Geometry handed to every kernel by value.
 struct Geo {

@@ -269,6 +269,7 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
     const long long n_src = (long long)g.B * g.G * g.sc * g.SP;
     gconv_kernel<T, T, false><<<grid_for(n_flt), kThreads, 0, st>>>(g, z, h, bias, g.relu, t1);
     fwd_out_kernel<T><<<grid_for(n_src), kThreads, 0, st>>>(g, x, t1, z, h, bias, out);
+    launched(2);
     return cudaGetLastError();
 }
 
@@ -284,18 +285,29 @@ cudaError_t backward(const Geo& g, const T* x, const T* z, const T* t1, const fl
     const long long n_src = (long long)g.B * g.G * g.sc * g.SP;
     bwd_ratio_kernel<T><<<grid_for(n_src), kThreads, 0, st>>>(g, x, t1, z, gout, h, bias, gnum,
                                                              gden, gz);
-    if (gz || gh)
+    launched();
+    if (gz || gh) {
         gconv_kernel<float, float, false><<<grid_for(n_flt), kThreads, 0, st>>>(g, gden, h, nullptr,
                                                                                0, gt1);
-    if (gx)
+        launched();
+    }
+    if (gx) {
         gconv_kernel<float, T, false><<<grid_for(n_flt), kThreads, 0, st>>>(g, gnum, h, nullptr, 0,
                                                                            gx);
-    if (gh)
+        launched();
+    }
+    if (gh) {
         wgrad_kernel<T><<<g.G * g.m * g.sc * g.KT, kThreads, 0, st>>>(g, x, t1, z, bias, gnum,
                                                                      gden, gt1, gh);
+        launched();
+    }
     if (gz) {
         gz_kernel<T><<<grid_for(n_src), kThreads, 0, st>>>(g, gt1, z, h, bias, gz);
-        if (gb) gb_kernel<T><<<g.G * g.sc, kThreads, 0, st>>>(g, gz, gb);
+        launched();
+        if (gb) {
+            gb_kernel<T><<<g.G * g.sc, kThreads, 0, st>>>(g, gz, gb);
+            launched();
+        }
     }
     return cudaGetLastError();
 }
@@ -310,6 +322,7 @@ cudaError_t gconv(const Geo& g, const T* in, const float* h, const float* bias, 
         const long long n = (long long)g.B * g.G * g.m * g.SP;
         gconv_kernel<T, T, false><<<grid_for(n), kThreads, 0, st>>>(g, in, h, bias, g.relu, out);
     }
+    launched();
     return cudaGetLastError();
 }
 

@@ -41,6 +41,44 @@ def force_generic(enabled: bool = True):
         _flags = old
 
 
+class _Timing:
+    """Optional CUDA-event timing of the C-ABI calls, on the stream they are issued on.
+
+    Off by default.  `enable()` starts collecting; `disable_and_collect()` synchronises and
+    returns ``{"ndc_fwd": [ms, ...], "ndc_bwd": [ms, ...]}``.
+    """
+
+    def __init__(self) -> None:
+        self.enabled = False
+        self._events = {"ndc_fwd": [], "ndc_bwd": []}
+
+    def enable(self) -> None:
+        self._events = {"ndc_fwd": [], "ndc_bwd": []}
+        self.enabled = True
+
+    @contextlib.contextmanager
+    def span(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record()
+        try:
+            yield
+        finally:
+            stop.record()
+            self._events[name].append((start, stop))
+
+    def disable_and_collect(self):
+        self.enabled = False
+        torch.cuda.synchronize()
+        return {k: [a.elapsed_time(b) for a, b in v] for k, v in self._events.items()}
+
+
+timing = _Timing()
+
+
 def kernels_apply(x: Tensor, m: int, sc: int, kernel_size: Sequence[int]) -> bool:
     """Whether the CUDA kernels cover this input and filter geometry.
 
@@ -118,8 +156,9 @@ class DeconvUpdate(torch.autograd.Function):
         if x.numel() and z.numel():
             with torch.cuda.device(x.device):
                 stream = torch.cuda.current_stream().cuda_stream
-                _lib.check(_lib.load().ndc_fwd(desc, _ptr(x), _ptr(z), _ptr(hf), _ptr(bf),
-                                               _ptr(out), _ptr(t1), stream))
+                with timing.span("ndc_fwd"):
+                    _lib.check(_lib.load().ndc_fwd(desc, _ptr(x), _ptr(z), _ptr(hf), _ptr(bf),
+                                                   _ptr(out), _ptr(t1), stream))
         ctx.cfg = (groups, m, sc, eps, relu_input)
         ctx.save_for_backward(x, z, t1, h, bias)
         return out
@@ -156,9 +195,10 @@ class DeconvUpdate(torch.autograd.Function):
                 nbytes = lib.ndc_bwd_workspace_bytes(desc)
                 ws = torch.empty(max(nbytes, 1), device=x.device, dtype=torch.uint8)
                 stream = torch.cuda.current_stream().cuda_stream
-                _lib.check(lib.ndc_bwd(desc, _ptr(x), _ptr(z), _ptr(t1), _ptr(hf), _ptr(bf),
-                                       _ptr(gout), _ptr(gx), _ptr(gz), _ptr(gh), _ptr(gb),
-                                       _ptr(ws), nbytes, stream))
+                with timing.span("ndc_bwd"):
+                    _lib.check(lib.ndc_bwd(desc, _ptr(x), _ptr(z), _ptr(t1), _ptr(hf), _ptr(bf),
+                                           _ptr(gout), _ptr(gx), _ptr(gz), _ptr(gh), _ptr(gb),
+                                           _ptr(ws), nbytes, stream))
                 # `ws` is released to the caching allocator here; later work on this stream
                 # is ordered after the kernels that use it
         else:

@@ -88,6 +88,10 @@ const char *ndc_last_error(void);
 /* Short name of a status code. */
 const char *ndc_status_string(int status);
 
+/* Number of kernel launches this library has issued in this process (all threads).  Lets a
+ * caller verify that the CUDA path, and not some other path, did the work. */
+uint64_t ndc_launch_count(void);
+
 /*
  * Whether a geometry is covered, and by which kernel family.  Returns NDC_OK and writes an
  * NdcPath to *path, or NDC_ERR_INVALID / NDC_ERR_UNSUPPORTED.  Host-only; no CUDA call.
