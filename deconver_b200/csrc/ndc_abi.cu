@@ -6,6 +6,7 @@
 #include "ndc_b200.h"
 #include "ndc_common.cuh"
 #include "ndc_generic.cuh"
+#include "ndc_dw4_host.cuh"
 
 namespace {
 
@@ -65,8 +66,8 @@ int check_ptr(const void* p, const char* name, int dtype) {
     } while (0)
 
 int path_of(const NdcDesc* d) {
-    (void)d;
-    return NDC_PATH_GENERIC;
+    if (d->flags & NDC_FLAG_FORCE_GENERIC) return NDC_PATH_GENERIC;
+    return ndc::dw4::covers(ndc::make_geo(*d, false)) ? NDC_PATH_DEPTHWISE4 : NDC_PATH_GENERIC;
 }
 
 }  // namespace
@@ -111,13 +112,24 @@ int ndc_fwd(const NdcDesc* desc, const void* x, const void* z, const float* h, c
     const ndc::Geo g = ndc::make_geo(*desc, bias != nullptr);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
+    typedef __nv_bfloat16 bf16;
+    if (path_of(desc) == NDC_PATH_DEPTHWISE4) {
+        bool handled = false;
+        if (desc->dtype == NDC_F32)
+            e = ndc::dw4::forward<float>(g, (const float*)x, (const float*)z, h, bias, (float*)out,
+                                         (float*)t1, desc->dtype, st, handled);
+        else
+            e = ndc::dw4::forward<bf16>(g, (const bf16*)x, (const bf16*)z, h, bias, (bf16*)out,
+                                        (bf16*)t1, desc->dtype, st, handled);
+        if (e != cudaSuccess) return cuda_fail(e, "ndc_fwd (depthwise) launch");
+        if (handled) return NDC_OK;
+    }
     if (desc->dtype == NDC_F32)
         e = ndc::generic::forward<float>(g, (const float*)x, (const float*)z, h, bias, (float*)out,
                                          (float*)t1, st);
     else
-        e = ndc::generic::forward<__nv_bfloat16>(g, (const __nv_bfloat16*)x,
-                                                 (const __nv_bfloat16*)z, h, bias,
-                                                 (__nv_bfloat16*)out, (__nv_bfloat16*)t1, st);
+        e = ndc::generic::forward<bf16>(g, (const bf16*)x, (const bf16*)z, h, bias, (bf16*)out,
+                                        (bf16*)t1, st);
     if (e != cudaSuccess) return cuda_fail(e, "ndc_fwd launch");
     return NDC_OK;
 }

@@ -281,3 +281,35 @@ def test_abi_status_codes_on_device(dev):
     assert lib.ndc_fwd(d, x.data_ptr() + 1, z.data_ptr(), h.data_ptr(), None, out.data_ptr(),
                        t1.data_ptr(), st) == 5
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("shape", [
+    (2, 64, (3, 3, 3), (64, 64, 64)),      # the 3-D benchmark geometry
+    (1, 32, (5, 5), (256, 256)),           # the 2-D benchmark geometry
+    (2, 32, (3, 3, 3), (24, 40, 72)),      # width not a power of two, several bands
+    (1, 8, (3, 3), (50, 132)),
+], ids=["cfg3", "cfg1", "odd3d", "odd2d"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_tiled_kernels_match_generic_kernels_at_full_size(dev, shape, dtype):
+    """At sizes the CPU oracle cannot finish quickly, the tiled depthwise kernels are checked
+    against the generic kernels (which the fixtures pin), forward and backward."""
+    B, C, ks, spatial = shape
+    gen = torch.Generator(device=dev).manual_seed(11)
+    x = torch.rand(B, C, *spatial, device=dev, generator=gen).to(dtype)
+    z = (torch.randn(B, 4 * C, *spatial, device=dev, generator=gen) * 0.5 + 0.3).to(dtype)
+    h = torch.rand(C, 4, *ks, device=dev, generator=gen) / float(np.prod(ks))
+    bias = torch.randn(4 * C, device=dev, generator=gen) * 0.1
+    gout = torch.randn(B, 4 * C, *spatial, device=dev, generator=gen).to(dtype)
+    cfg = dict(groups=C, m=1, sc=4, eps=1e-16, relu_input=True)
+    res = []
+    for generic in (True, False):
+        t = [v.clone().requires_grad_(True) for v in (x, z, h, bias)]
+        with Fn.force_generic(generic):
+            out = dcb.deconv_update(*t, **cfg)
+            out.backward(gout)
+        res.append([out.detach()] + [v.grad for v in t])
+    torch.cuda.synchronize()
+    tol = F32_TOL if dtype == torch.float32 else BF16_TOL
+    for name, a, b in zip(("out", "gx", "gz", "gh", "gb"), res[1], res[0]):
+        err = max_norm_error(a.float().cpu().numpy(), b.float().cpu().numpy())
+        assert err < tol, f"{name} error {err:.3e}"
