@@ -352,6 +352,34 @@ def run_b200(args):
     print(json.dumps(line), flush=True)
 
 
+def run_profile_case(args):
+    """A small, bounded run of the update for `ncu`: the benchmark geometry at batch
+    `--batch` (default 1), `--steps` forward+backward calls, nothing else."""
+    import deconver_b200 as dcb
+
+    dev = torch.device("cuda", 0)
+    dcb.load_library()
+    C, r, ks, S = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"], WORKLOAD["spatial"]
+    B = args.batch
+    dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.rand(B, C, *S, device=dev, generator=gen).to(dt).requires_grad_(True)
+    z = (torch.randn(B, C * r, *S, device=dev, generator=gen) * 0.5 + 0.3).to(dt).requires_grad_(True)
+    h = (torch.randn(C, r, *ks, device=dev, generator=gen).abs() / 27).requires_grad_(True)
+    b = (torch.randn(C * r, device=dev, generator=gen) * 0.1).requires_grad_(True)
+    g = torch.randn(B, C * r, *S, device=dev, generator=gen).to(dt)
+    from deconver_b200 import functional as Fn
+    Fn.timing.enable()
+    for _ in range(args.steps):
+        out = dcb.deconv_update(x, z, h, b, groups=C, m=1, sc=r, eps=1e-16, relu_input=True)
+        out.backward(g)
+        x.grad = z.grad = h.grad = b.grad = None
+    ms = Fn.timing.disable_and_collect()
+    print(json.dumps({"profile_case": True, "batch": B, "steps": args.steps, "dtype": args.dtype,
+                      "ndc_fwd_ms": [round(v, 4) for v in ms["ndc_fwd"]],
+                      "ndc_bwd_ms": [round(v, 4) for v in ms["ndc_bwd"]]}))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--gpus", type=int, default=1)
@@ -360,8 +388,14 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--profile-case", action="store_true",
+                    help="run only a few update calls at --batch (for an ncu capture)")
+    ap.add_argument("--batch", type=int, default=1, help="batch of --profile-case")
+    ap.add_argument("--dtype", choices=["f32", "bf16"], default="f32", help="dtype of --profile-case")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

@@ -2,14 +2,16 @@
 //
 // Work decomposition.  One CTA owns one (sample, group) pair, a band of TH rows spanning the
 // full width W, and a chunk of DC planes, and marches through the chunk plane by plane.
-// Planes live in shared memory as float32 rows of `pitch = 8*NS + 8` floats, NS = ceil(W/8)
-// strips of 8 voxels; shared column c holds w = c - 4, so rows are 16-byte aligned and the
-// four columns on either side are the zero padding of the volume.  Within a row the 16-byte
-// quads are XOR-swizzled (`swz`) so that a quarter-warp of consecutive strips reads eight
-// distinct bank groups.
+// Planes live in shared memory as float32 rows of `pitch` floats.  Shared column c holds
+// w = c - (4 + PW), PW = kW/2: with that shift the inputs of a strip that starts at a
+// multiple of 4 begin on a 16-byte quad, so a strip's window is read as whole quads:
 //
-// A thread's unit of work is a strip: 8 consecutive voxels of one row.  The 8 + 2*pad
-// inputs a strip needs are read as four aligned quads (16 floats) covering w0-4 .. w0+11.
+//   A-type sweep (adjoint taps, many accumulators): strips of 4 voxels, window = 2 quads
+//   K-type sweep (rolling sums along depth, few accumulators): strips of 8, window = 3 quads
+//
+// Rows read by 8-voxel strips are XOR-swizzled at quad granularity (`SWZ`), so that the eight
+// lanes of a quarter-warp, two quads apart, hit eight distinct bank groups; rows read by
+// 4-voxel strips are consecutive quads already and stay linear.
 #pragma once
 
 #include "ndc_common.cuh"
@@ -17,39 +19,53 @@
 namespace ndc {
 namespace dw4 {
 
-constexpr int V = 8;     // voxels per strip
 constexpr int SCH = 4;   // source channels per group
-constexpr int ORG = 4;   // shared column of w = 0
+constexpr int VA = 4;    // voxels per strip, A-type sweeps
+constexpr int VK = 8;    // voxels per strip, K-type sweeps
 
 // Host-side tiling decision for one geometry.
 struct Tiling {
-    int NS;     // strips per row
+    int NQ;     // quads (4 voxels) per row = ceil(W/4)
     int pitch;  // floats per shared-memory row
     int TH;     // rows per band
     int nth;    // bands along H
     int DC;     // planes per chunk
     int ndc;    // chunks along D
-    int vec;    // rows of the global tensors are 16-byte aligned: vector loads and stores
 };
 
-__device__ __forceinline__ int swz(int quad) { return quad ^ ((quad >> 3) & 1); }
+// floats per shared row: the data quads, one quad of left margin, and enough on the right for
+// the last strip's window (3 quads past an 8-strip start, rounded to an even quad count)
+__host__ __device__ inline int row_pitch(int W) {
+    const int nq = (W + 3) / 4;
+    const int ns8 = (nq + 1) / 2;
+    return 4 * (2 * ns8 + 4);
+}
 
-// Float offset, within a row, of the quad that holds shared column `col` (col % 4 == 0).
-__device__ __forceinline__ int quad_off(int col) { return swz(col >> 2) << 2; }
+template <bool SWZ> __device__ __forceinline__ int phys_quad(int quad) {
+    return SWZ ? (quad ^ ((quad >> 3) & 1)) : quad;
+}
 
-// The 16 floats w0-4 .. w0+11 of a row (w0 = 8*strip), as four swizzled quads.
-__device__ __forceinline__ void load_window(const float* row, int strip, float (&v)[16]) {
+// NQW consecutive quads of a shared row starting at quad `first`.
+template <int NQW, bool SWZ>
+__device__ __forceinline__ void load_window(const float* row, int first, float (&v)[4 * NQW]) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        const float4 t = *reinterpret_cast<const float4*>(row + (swz(2 * strip + q) << 2));
+    for (int q = 0; q < NQW; ++q) {
+        const float4 t = *reinterpret_cast<const float4*>(row + (phys_quad<SWZ>(first + q) << 2));
         v[4 * q + 0] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
     }
 }
 
-// Store the 8 voxels of a strip into a shared row.
-__device__ __forceinline__ void store_strip(float* row, int strip, const float (&v)[V]) {
-    *reinterpret_cast<float4*>(row + (swz(2 * strip + 1) << 2)) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(row + (swz(2 * strip + 2) << 2)) = make_float4(v[4], v[5], v[6], v[7]);
+// Shared float offset (within a row) of column `col`.
+template <bool SWZ> __device__ __forceinline__ int col_off(int col) {
+    return (phys_quad<SWZ>(col >> 2) << 2) | (col & 3);
+}
+
+// Store N voxels starting at volume column w0 into a shared row (scalar: the column shift
+// makes these stores unaligned).
+template <int N, int PW, bool SWZ>
+__device__ __forceinline__ void store_strip(float* row, int w0, const float (&v)[N]) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) row[col_off<SWZ>(w0 + 4 + PW + i)] = v[i];
 }
 
 // Four consecutive elements of a global row, converted to float32.  `n` of them are inside
@@ -118,21 +134,22 @@ __device__ __forceinline__ void store4<__nv_bfloat16, false>(__nv_bfloat16* p, i
     if (n > 3) p[3] = __float2bfloat16_rn(v.w);
 }
 
-// Load / store the 8 voxels of a strip of a global row; elements at w >= W are 0 / skipped.
-template <typename T, bool VEC>
-__device__ __forceinline__ void load_strip_global(const T* row, int w0, int W, float (&v)[V]) {
+// Load / store N (a multiple of 4) voxels of a global row from column w0; elements at
+// w >= W read as 0 / are skipped.
+template <typename T, bool VEC, int N>
+__device__ __forceinline__ void load_strip_global(const T* row, int w0, int W, float (&v)[N]) {
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
+    for (int q = 0; q < N / 4; ++q) {
         const int w = w0 + 4 * q, n = W - w;
         float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
         if (n > 0) t = load4<T, VEC>(row + w, n < 4 ? n : 4);
         v[4 * q + 0] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
     }
 }
-template <typename T, bool VEC>
-__device__ __forceinline__ void store_strip_global(T* row, int w0, int W, const float (&v)[V]) {
+template <typename T, bool VEC, int N>
+__device__ __forceinline__ void store_strip_global(T* row, int w0, int W, const float (&v)[N]) {
 #pragma unroll
-    for (int q = 0; q < 2; ++q) {
+    for (int q = 0; q < N / 4; ++q) {
         const int w = w0 + 4 * q, n = W - w;
         if (n > 0)
             store4<T, VEC>(row + w, n < 4 ? n : 4,
@@ -141,32 +158,50 @@ __device__ __forceinline__ void store_strip_global(T* row, int w0, int W, const 
 }
 
 // Plane loader.  A plane region of `rows` rows is cut into chunks of 4 consecutive elements;
-// chunk -> (row, quad) decoding is done once per CTA into a descriptor table in shared
-// memory: .x = element offset inside the plane (or -1 for a row outside the volume, which
-// stays zero), .y = float offset inside the shared plane | (valid elements << 24).
+// chunk -> (channel, row, quad) decoding is done once per CTA into a descriptor table in
+// shared memory: .goff = element offset inside the plane (or -1 for a row outside the
+// volume, which stays zero); .soff = float offset of the shared ROW | (volume column << 16)
+// | (valid elements << 26) | (channel << 29).
 struct ChunkDesc { int goff, soff; };
+__device__ __forceinline__ int desc_row(int soff) { return soff & 0xffff; }
+__device__ __forceinline__ int desc_w(int soff) { return (soff >> 16) & 0x3ff; }
+__device__ __forceinline__ int desc_n(int soff) { return (soff >> 26) & 7; }
+__device__ __forceinline__ int desc_ch(int soff) { return (soff >> 29) & 3; }
 
-__device__ __forceinline__ void build_descs(ChunkDesc* tab, int channels, int rows, int NS,
+__device__ __forceinline__ void build_descs(ChunkDesc* tab, int channels, int rows, int NQ,
                                             int pitch, int h_first, int H, int W, long long SP,
                                             int nthreads) {
-    const int per_row = 2 * NS;
-    const int total = channels * rows * per_row;
+    const int total = channels * rows * NQ;
     for (int id = threadIdx.x; id < total; id += nthreads) {
-        const int c4 = id % per_row;
-        const int t = id / per_row;
+        const int c4 = id % NQ;
+        const int t = id / NQ;
         const int r = t % rows, ch = t / rows;
         const int h = h_first + r, w = 4 * c4;
         ChunkDesc d;
         const int n = W - w;
-        if (h < 0 || h >= H || n <= 0) {
+        if (h < 0 || h >= H) {
             d.goff = -1; d.soff = 0;
         } else {
             d.goff = (int)(ch * SP) + h * W + w;
-            d.soff = ((ch * rows + r) * pitch + quad_off(w + ORG)) | ((n < 4 ? n : 4) << 24);
+            d.soff = ((ch * rows + r) * pitch) | (w << 16) | ((n < 4 ? n : 4) << 26) | (ch << 29);
         }
         tab[id] = d;
     }
 }
+
+// Write a chunk's 4 values into its shared row at columns w+4+PW .. (unaligned by PW).
+template <int PW, bool SWZ>
+__device__ __forceinline__ void stage_chunk(float* plane, int soff, float4 v) {
+    float* row = plane + desc_row(soff);
+    const int c = desc_w(soff) + 4 + PW;
+    row[col_off<SWZ>(c)] = v.x;
+    row[col_off<SWZ>(c + 1)] = v.y;
+    row[col_off<SWZ>(c + 2)] = v.z;
+    row[col_off<SWZ>(c + 3)] = v.w;
+}
+
+// x / (y) with one reciprocal approximation: |relative error| <= 2 ulp, y > 0 and normal.
+__device__ __forceinline__ float fast_div(float x, float y) { return __fdividef(x, y); }
 
 }  // namespace dw4
 }  // namespace ndc

@@ -6,12 +6,13 @@
 // chunk and keeps the planes it needs in shared-memory rings.  Per step p (a source plane):
 //
 //   prefetch   z plane p+1 and x plane p-PD into registers (global loads in flight)
-//   K phase    every K-thread owns a strip of the t1 band (TH + 2*PH rows) and keeps KD
-//              running sums, one per t1 plane that source plane p contributes to; plane
+//   K phase    every K-thread owns an 8-voxel strip of the t1 band (TH + 2*PH rows) and keeps
+//              KD running sums, one per t1 plane that source plane p contributes to; plane
 //              p-PD is complete after this step and goes to the t1 ring (and to HBM)
 //   stage      the prefetched planes are rectified/biased and written to shared memory
 //   barrier
-//   A phase    output plane d = p-2*PD: A(x) and A(t1) from the rings, epilogue, store
+//   A phase    output plane d = p-2*PD, 4-voxel strips: A(x) and A(t1) from the rings,
+//              epilogue, store
 //
 // One barrier per step: the s buffer is double-buffered and both rings hold KD+1 planes, so
 // whatever a fast thread writes in step p+1 is never what a slow thread still reads in p.
@@ -34,11 +35,10 @@ struct FwdParams {
 template <int KD, int KH, int KW>
 struct FwdSmem {
     static constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
-    static constexpr int WKP = (KD * KW + 3) / 4 * 4;  // padded weights per (kh, j) in the K layout
-    static constexpr int RING = KD > 1 ? KD + 1 : 1;  // planes per ring
-    static constexpr int NSB = KD > 1 ? 2 : 1;        // source buffers
-    // float offsets
-    int wA, wK, sbuf, t1ring, xring, zdesc, xdesc, total_floats;
+    static constexpr int WKP = (KD * KW + 3) / 4 * 4;  // padded weights per (kh, j), K layout
+    static constexpr int RING = KD > 1 ? KD + 1 : 1;   // planes per ring
+    static constexpr int NSB = KD > 1 ? 2 : 1;         // source buffers
+    int wA, wK, sbuf, t1ring, xring, zdesc, xdesc, total_floats;  // float offsets
     int RS, RT, plane_s, plane_t;
     __host__ __device__ FwdSmem(const Tiling& t) {
         RS = t.TH + 4 * PH;
@@ -52,22 +52,23 @@ struct FwdSmem {
         sbuf = o; o += NSB * plane_s;
         t1ring = o; o += RING * plane_t;
         xring = o; o += RING * plane_t;
-        zdesc = o; o += 2 * (SCH * RS * 2 * t.NS);
-        xdesc = o; o += 2 * (RT * 2 * t.NS);
+        zdesc = o; o += KD > 1 ? 2 * (SCH * RS * t.NQ) : 0;  // loader tables: marching kernels only
+        xdesc = o; o += KD > 1 ? 2 * (RT * t.NQ) : 0;
         total_floats = o;
     }
 };
 
-template <typename T, int KD, int KH, int KW, int NT, int RK, int RA, int MAXZ, int MAXX, int MINB,
-          bool VEC>
+template <typename T, int KD, int KH, int KW, int NT, int MAXZ, int MAXX, int MINB, bool VEC>
 __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = FwdSmem<KD, KH, KW>;
     constexpr int WKP = L::WKP, RING = L::RING, NSB = L::NSB;
+    constexpr int NQK = 2 + (2 * PW + 3) / 4;   // quads in an 8-strip window (8 + 2*PW floats)
+    constexpr int NQA = 1 + (2 * PW + 3) / 4;   // quads in a 4-strip window (4 + 2*PW floats)
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
     const int tid = threadIdx.x;
-    const int NS = P.t.NS, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const int NQ = P.t.NQ, NS8 = (NQ + 1) / 2, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
     const long long HW = (long long)H * W, SP = HW * D;
 
     // ---- which work item
@@ -112,63 +113,40 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             wK[i] = v;
         }
     }
-    const int nz = SCH * RS * 2 * NS, nx = RT * 2 * NS;
-    build_descs(zdesc, SCH, RS, NS, pitch, h0 - 2 * PH, H, W, SP, NT);
-    build_descs(xdesc, 1, RT, NS, pitch, h0 - PH, H, W, SP, NT);
+    const int nz = SCH * RS * NQ, nx = RT * NQ;
+    if (KD > 1) {
+        build_descs(zdesc, SCH, RS, NQ, pitch, h0 - 2 * PH, H, W, SP, NT);
+        build_descs(xdesc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
+    }
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
 
-    // ---- this thread's strips
-    int k_row[RK], k_strip[RK]; bool k_ok[RK];
-    float kacc[RK][KD][V];
+    // ---- this thread's K strip (8 voxels of one row of the t1 band) and its running sums
+    const int k_row = tid / NS8, k_strip = tid % NS8;
+    const bool k_ok = tid < (TH + 2 * PH) * NS8 && h0 - PH + k_row >= 0 && h0 - PH + k_row < H;
+    float kacc[KD][VK];
 #pragma unroll
-    for (int r = 0; r < RK; ++r) {
-        const int item = tid + r * NT;
-        k_row[r] = item / NS; k_strip[r] = item % NS;
-        const int h = h0 - PH + k_row[r];
-        k_ok[r] = item < (TH + 2 * PH) * NS && h >= 0 && h < H;
+    for (int a = 0; a < KD; ++a)
 #pragma unroll
-        for (int a = 0; a < KD; ++a)
-#pragma unroll
-            for (int v = 0; v < V; ++v) kacc[r][a][v] = 0.0f;
-    }
-    int a_row[RA], a_strip[RA]; bool a_ok[RA];
-#pragma unroll
-    for (int r = 0; r < RA; ++r) {
-        const int item = tid + r * NT;
-        a_row[r] = item / NS; a_strip[r] = item % NS;
-        a_ok[r] = item < TH * NS;
-    }
+        for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
+    const int a_items = TH * NQ;
     __syncthreads();
 
-    // stage helpers ----------------------------------------------------------------------
-    auto stage_z = [&](const float4 (&reg)[MAXZ], int plane) {
-        float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
-#pragma unroll
-        for (int i = 0; i < MAXZ; ++i) {
-            const int id = tid + i * NT;
-            if (id < nz) {
-                const ChunkDesc dsc = zdesc[id];
-                if (dsc.goff >= 0) {
-                    const int so = dsc.soff & 0xffffff, n = dsc.soff >> 24;
-                    const int j = id / (RS * 2 * NS);
-                    const float b = j == 0 ? bj[0] : j == 1 ? bj[1] : j == 2 ? bj[2] : bj[3];
-                    float4 v = reg[i];
-                    v.x += b; v.y += b; v.z += b; v.w += b;
-                    if (P.relu) {
-                        v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f);
-                        v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
-                    }
-                    if (n < 4) {  // elements past the end of the row stay zero
-                        if (n < 2) v.y = 0.f;
-                        if (n < 3) v.z = 0.f;
-                        v.w = 0.f;
-                    }
-                    *reinterpret_cast<float4*>(dst + so) = v;
-                }
-            }
+    auto rectify = [&](float4 v, int soff) {
+        const int j = desc_ch(soff), n = desc_n(soff);
+        const float b = j == 0 ? bj[0] : j == 1 ? bj[1] : j == 2 ? bj[2] : bj[3];
+        v.x += b; v.y += b; v.z += b; v.w += b;
+        if (P.relu) {
+            v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f);
+            v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
         }
+        if (n < 4) {  // elements past the end of the row stay zero
+            if (n < 2) v.y = 0.f;
+            if (n < 3) v.z = 0.f;
+            v.w = 0.f;
+        }
+        return v;
     };
     auto fetch_z = [&](float4 (&reg)[MAXZ], int plane) {
         const T* src = zg + (long long)plane * HW;
@@ -177,7 +155,18 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int id = tid + i * NT;
             if (id < nz) {
                 const ChunkDesc dsc = zdesc[id];
-                if (dsc.goff >= 0) reg[i] = load4<T, VEC>(src + dsc.goff, dsc.soff >> 24);
+                if (dsc.goff >= 0) reg[i] = load4<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
+            }
+        }
+    };
+    auto stage_z = [&](const float4 (&reg)[MAXZ], int plane) {
+        float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
+#pragma unroll
+        for (int i = 0; i < MAXZ; ++i) {
+            const int id = tid + i * NT;
+            if (id < nz) {
+                const ChunkDesc dsc = zdesc[id];
+                if (dsc.goff >= 0) stage_chunk<PW, true>(dst, dsc.soff, rectify(reg[i], dsc.soff));
             }
         }
     };
@@ -188,7 +177,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int id = tid + i * NT;
             if (id < nx) {
                 const ChunkDesc dsc = xdesc[id];
-                if (dsc.goff >= 0) reg[i] = load4<T, VEC>(src + dsc.goff, dsc.soff >> 24);
+                if (dsc.goff >= 0) reg[i] = load4<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
             }
         }
     };
@@ -199,48 +188,37 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int id = tid + i * NT;
             if (id < nx) {
                 const ChunkDesc dsc = xdesc[id];
-                if (dsc.goff >= 0)
-                    *reinterpret_cast<float4*>(dst + (dsc.soff & 0xffffff)) = reg[i];
+                if (dsc.goff >= 0) stage_chunk<PW, false>(dst, dsc.soff, reg[i]);
             }
         }
     };
-    const int qbase = d0 - 3 * PD - 1;  // ring slot of plane q is (q - qbase) % RING
-    auto slot_of = [&](int q) { return (q - qbase) % RING; };
-
-    // plane loads without prefetch (prologue; the only loads of a 2-D problem)
+    // plane loads without prefetch (prologue; the only loads of a 2-D problem): chunks are
+    // decoded on the fly
     auto load_z_now = [&](int plane) {
         const T* src = zg + (long long)plane * HW;
         float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
         for (int id = tid; id < nz; id += NT) {
-            const ChunkDesc dsc = zdesc[id];
-            if (dsc.goff < 0) continue;
-            const int so = dsc.soff & 0xffffff, n = dsc.soff >> 24;
-            const int j = id / (RS * 2 * NS);
-            const float b = j == 0 ? bj[0] : j == 1 ? bj[1] : j == 2 ? bj[2] : bj[3];
-            float4 v = load4<T, VEC>(src + dsc.goff, n);
-            v.x += b; v.y += b; v.z += b; v.w += b;
-            if (P.relu) {
-                v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f);
-                v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
-            }
-            if (n < 4) {
-                if (n < 2) v.y = 0.f;
-                if (n < 3) v.z = 0.f;
-                v.w = 0.f;
-            }
-            *reinterpret_cast<float4*>(dst + so) = v;
+            const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
+            const int h = h0 - 2 * PH + r, w = 4 * c4, n = min(4, W - w);
+            if (h < 0 || h >= H) continue;
+            const int soff = ((ch * RS + r) * pitch) | (w << 16) | (n << 26) | (ch << 29);
+            const float4 v = load4<T, VEC>(src + ch * SP + (long long)h * W + w, n);
+            stage_chunk<PW, true>(dst, soff, rectify(v, soff));
         }
     };
     auto load_x_now = [&](int plane, int slot) {
         const T* src = xg + (long long)plane * HW;
         float* dst = xring + slot * lay.plane_t;
         for (int id = tid; id < nx; id += NT) {
-            const ChunkDesc dsc = xdesc[id];
-            if (dsc.goff < 0) continue;
-            *reinterpret_cast<float4*>(dst + (dsc.soff & 0xffffff)) =
-                load4<T, VEC>(src + dsc.goff, dsc.soff >> 24);
+            const int c4 = id % NQ, r = id / NQ;
+            const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
+            if (h < 0 || h >= H) continue;
+            const int soff = (r * pitch) | (w << 16) | (n << 26);
+            stage_chunk<PW, false>(dst, soff, load4<T, VEC>(src + (long long)h * W + w, n));
         }
     };
+    const int qbase = d0 - 3 * PD - 1;  // ring slot of plane q is (q - qbase) % RING
+    auto slot_of = [&](int q) { return (q - qbase) % RING; };
 
     // ---- prologue: first source plane
     const int p_first = d0 - 2 * PD, p_last = d1 - 1 + 2 * PD;
@@ -261,53 +239,67 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         const bool s_ok = p >= 0 && p < D;
         const int qdone = p - PD;  // t1 plane completed by this step
         const bool q_need = qdone >= d0 - PD && qdone <= d1 - 1 + PD && qdone >= 0 && qdone < D;
+        auto k_accumulate = [&](int row, int strip, float (&acc)[KD][VK]) {
+            const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + row * pitch;
+            // rolled on purpose: the body is the unit the instruction cache holds
+#pragma unroll 1
+            for (int kh = 0; kh < KH; ++kh) {
+#pragma unroll 1
+                for (int j = 0; j < SCH; ++j) {
+                    float sv[4 * NQK];
+                    load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
+                    float w[WKP];
 #pragma unroll
-        for (int r = 0; r < RK; ++r) {
-            if (k_ok[r]) {
-                if (s_ok) {
-                    const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + k_row[r] * pitch;
-#pragma unroll
-                    for (int kh = 0; kh < KH; ++kh) {
-#pragma unroll
-                        for (int j = 0; j < SCH; ++j) {
-                            float sv[16];
-                            load_window(sp + (j * RS + kh) * pitch, k_strip[r], sv);
-                            float w[WKP];
-#pragma unroll
-                            for (int q4 = 0; q4 < WKP / 4; ++q4) {
-                                const float4 t = *reinterpret_cast<const float4*>(
-                                    wK + (kh * SCH + j) * WKP + 4 * q4);
-                                w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
-                            }
-#pragma unroll
-                            for (int kd = 0; kd < KD; ++kd)
-#pragma unroll
-                                for (int kw = 0; kw < KW; ++kw)
-#pragma unroll
-                                    for (int v = 0; v < V; ++v)
-                                        kacc[r][kd][v] = fmaf(sv[ORG + v + kw - PW], w[kd * KW + kw],
-                                                              kacc[r][kd][v]);
-                        }
+                    for (int q4 = 0; q4 < WKP / 4; ++q4) {
+                        const float4 t = *reinterpret_cast<const float4*>(
+                            wK + (kh * SCH + j) * WKP + 4 * q4);
+                        w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
                     }
-                }
-                if (q_need) {
-                    const int w0 = V * k_strip[r];
-                    float tv[V];
 #pragma unroll
-                    for (int v = 0; v < V; ++v) tv[v] = (w0 + v < W) ? kacc[r][KD - 1][v] : 0.0f;
-                    store_strip(t1ring + slot_of(qdone) * lay.plane_t + k_row[r] * pitch, k_strip[r], tv);
-                    const int h = h0 - PH + k_row[r];
-                    if (qdone >= d0 && qdone < d1 && k_row[r] >= PH && k_row[r] < PH + TH)
-                        store_strip_global<T, VEC>(tg + (long long)qdone * HW + (long long)h * W, w0, W, tv);
+                    for (int kd = 0; kd < KD; ++kd)
+#pragma unroll
+                        for (int kw = 0; kw < KW; ++kw)
+#pragma unroll
+                            for (int v = 0; v < VK; ++v)
+                                acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
                 }
+            }
+        };
+        auto k_finish = [&](int row, int strip, const float (&done)[VK]) {
+            const int w0 = VK * strip;
+            float tv[VK];
+#pragma unroll
+            for (int v = 0; v < VK; ++v) tv[v] = (w0 + v < W) ? done[v] : 0.0f;
+            store_strip<VK, PW, false>(t1ring + slot_of(qdone) * lay.plane_t + row * pitch, w0, tv);
+            const int h = h0 - PH + row;
+            if (qdone >= d0 && qdone < d1 && row >= PH && row < PH + TH)
+                store_strip_global<T, VEC, VK>(tg + (long long)qdone * HW + (long long)h * W, w0, W, tv);
+        };
+        if (KD > 1) {
+            if (k_ok) {
+                if (s_ok) k_accumulate(k_row, k_strip, kacc);
+                if (q_need) k_finish(k_row, k_strip, kacc[KD - 1]);
             }
             // rotate the running sums: slot kd now stands for plane (p+1)+PD-kd
 #pragma unroll
             for (int kd = KD - 1; kd > 0; --kd)
 #pragma unroll
-                for (int v = 0; v < V; ++v) kacc[r][kd][v] = kacc[r][kd - 1][v];
+                for (int v = 0; v < VK; ++v) kacc[kd][v] = kacc[kd - 1][v];
 #pragma unroll
-            for (int v = 0; v < V; ++v) kacc[r][0][v] = 0.0f;
+            for (int v = 0; v < VK; ++v) kacc[0][v] = 0.0f;
+        } else if (s_ok && q_need) {
+            // no depth taps: nothing persists between planes, so strips are simply looped over
+#pragma unroll 1
+            for (int item = tid; item < (TH + 2 * PH) * NS8; item += NT) {
+                const int row = item / NS8, strip = item % NS8;
+                const int h = h0 - PH + row;
+                if (h < 0 || h >= H) continue;
+                float acc[KD][VK];
+#pragma unroll
+                for (int v = 0; v < VK; ++v) acc[0][v] = 0.0f;
+                k_accumulate(row, strip, acc);
+                k_finish(row, strip, acc[KD - 1]);
+            }
         }
 
         // -------- stage the prefetched planes
@@ -318,30 +310,31 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         // -------- A phase: output plane d
         const int d = p - 2 * PD;
         if (d < d0 || d >= d1) continue;
-#pragma unroll
-        for (int r = 0; r < RA; ++r) {
-            if (!a_ok[r]) continue;
-            const int hrow = h0 + a_row[r], w0 = V * a_strip[r];
-            float zv[SCH][V];
-#pragma unroll
-            for (int j = 0; j < SCH; ++j)
-                load_strip_global<T, VEC>(zg + j * SP + (long long)d * HW + (long long)hrow * W, w0, W, zv[j]);
-            float an[SCH][V], ad[SCH][V];
+#pragma unroll 1
+        for (int item = tid; item < a_items; item += NT) {
+            const int a_row = item / NQ, a_q = item % NQ;
+            const int hrow = h0 + a_row, w0 = VA * a_q;
+            float zv[SCH][VA];
 #pragma unroll
             for (int j = 0; j < SCH; ++j)
+                load_strip_global<T, VEC, VA>(zg + j * SP + (long long)d * HW + (long long)hrow * W,
+                                              w0, W, zv[j]);
+            float an[SCH][VA], ad[SCH][VA];
 #pragma unroll
-                for (int v = 0; v < V; ++v) { an[j][v] = P.eps; ad[j][v] = P.eps; }
+            for (int j = 0; j < SCH; ++j)
 #pragma unroll
+                for (int v = 0; v < VA; ++v) { an[j][v] = P.eps; ad[j][v] = P.eps; }
+#pragma unroll 1
             for (int kd = 0; kd < KD; ++kd) {
                 const int q = d + PD - kd;
                 if (q < 0 || q >= D) continue;
                 const int slot = slot_of(q);
 #pragma unroll
                 for (int kh = 0; kh < KH; ++kh) {
-                    const int rr = a_row[r] + PH + PH - kh;  // ring row of h + PH - kh
-                    float xv[16], tv[16];
-                    load_window(xring + slot * lay.plane_t + rr * pitch, a_strip[r], xv);
-                    load_window(t1ring + slot * lay.plane_t + rr * pitch, a_strip[r], tv);
+                    const int rr = a_row + PH + PH - kh;  // ring row of h + PH - kh
+                    float xv[4 * NQA], tv[4 * NQA];
+                    load_window<NQA, false>(xring + slot * lay.plane_t + rr * pitch, a_q + 1, xv);
+                    load_window<NQA, false>(t1ring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
 #pragma unroll
                     for (int kw = 0; kw < KW; ++kw) {
                         const float4 w4 = *reinterpret_cast<const float4*>(
@@ -350,23 +343,24 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
 #pragma unroll
                         for (int j = 0; j < SCH; ++j)
 #pragma unroll
-                            for (int v = 0; v < V; ++v) {
-                                an[j][v] = fmaf(xv[ORG + v + PW - kw], wj[j], an[j][v]);
-                                ad[j][v] = fmaf(tv[ORG + v + PW - kw], wj[j], ad[j][v]);
+                            for (int v = 0; v < VA; ++v) {
+                                an[j][v] = fmaf(xv[v + 2 * PW - kw], wj[j], an[j][v]);
+                                ad[j][v] = fmaf(tv[v + 2 * PW - kw], wj[j], ad[j][v]);
                             }
                     }
                 }
             }
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                float ov[V];
+                float ov[VA];
 #pragma unroll
-                for (int v = 0; v < V; ++v) {
+                for (int v = 0; v < VA; ++v) {
                     float s = zv[j][v] + bj[j];
                     if (P.relu) s = fmaxf(s, 0.0f);
-                    ov[v] = __fdividef(s * an[j][v], ad[j][v]);
+                    ov[v] = fast_div(s * an[j][v], ad[j][v]);
                 }
-                store_strip_global<T, VEC>(og + j * SP + (long long)d * HW + (long long)hrow * W, w0, W, ov);
+                store_strip_global<T, VEC, VA>(og + j * SP + (long long)d * HW + (long long)hrow * W,
+                                               w0, W, ov);
             }
         }
     }

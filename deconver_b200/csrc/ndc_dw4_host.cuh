@@ -1,6 +1,8 @@
 // Host side of the tiled depthwise kernels: tiling decisions and launches.
 #pragma once
 
+#include <algorithm>
+
 #include "ndc_dw4_fwd.cuh"
 
 namespace ndc {
@@ -12,13 +14,27 @@ constexpr size_t kSmemMax = 227 * 1024;
 
 // Launch shape per kernel geometry.
 template <int KD, int KH, int KW> struct FwdShape;
-template <> struct FwdShape<3, 3, 3> { static constexpr int NT = 160, RK = 1, RA = 1, MAXZ = 8, MAXX = 2, MINB = 2; };
-template <> struct FwdShape<1, 5, 5> { static constexpr int NT = 256, RK = 2, RA = 2, MAXZ = 1, MAXX = 1, MINB = 1; };
-template <> struct FwdShape<1, 3, 3> { static constexpr int NT = 256, RK = 2, RA = 2, MAXZ = 1, MAXX = 1, MINB = 1; };
+template <> struct FwdShape<3, 3, 3> { static constexpr int NT = 256, MAXZ = 5, MAXX = 1, MINB = 2; };
+template <> struct FwdShape<1, 5, 5> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
+template <> struct FwdShape<1, 3, 3> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
 
 inline bool shape_supported(int kD, int kH, int kW) {
     return (kD == 3 && kH == 3 && kW == 3) || (kD == 1 && kH == 5 && kW == 5) ||
            (kD == 1 && kH == 3 && kW == 3);
+}
+
+// Chunks along depth: enough CTAs for about `waves` rounds of two CTAs per SM, but chunks of
+// at least 16 planes (every chunk recomputes 2*PD planes of its neighbours).
+inline void plan_depth(int KD, int D, long long ctas_per_chunk, int waves, Tiling& t) {
+    if (KD == 1) {
+        t.DC = 1;
+    } else {
+        const long long target = (long long)waves * 2 * kNumSMs;
+        long long ndc = target / std::max(1LL, ctas_per_chunk);
+        ndc = std::max(1LL, std::min(ndc, (long long)std::max(1, D / 16)));
+        t.DC = (int)((D + ndc - 1) / ndc);
+    }
+    t.ndc = (D + t.DC - 1) / t.DC;
 }
 
 template <int KD, int KH, int KW>
@@ -26,33 +42,25 @@ inline bool plan_fwd(int D, int H, int W, long long BC, Tiling& t, size_t& smem_
     using S = FwdShape<KD, KH, KW>;
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29)) return false;  // 32-bit offsets inside a slab
-    t.NS = (W + V - 1) / V;
-    if (t.NS > 32) return false;
-    t.pitch = V * t.NS + 8;
-    int TH = S::NT * S::RK / t.NS - 2 * PH;
-    TH = min(TH, S::NT * S::RA / t.NS);
+    if (W > 256) return false;
+    t.NQ = (W + 3) / 4;
+    t.pitch = row_pitch(W);
+    const int NS8 = (t.NQ + 1) / 2;
+    int TH = H;
     if (KD > 1) {
-        TH = min(TH, S::NT * S::MAXZ / (8 * t.NS) - 4 * PH);
-        TH = min(TH, S::NT * S::MAXX / (2 * t.NS) - 2 * PH);
+        TH = std::min(TH, S::NT / NS8 - 2 * PH);                         // one K strip per thread
+        TH = std::min(TH, S::NT * S::MAXZ / (SCH * t.NQ) - 4 * PH);      // z prefetch registers
+        TH = std::min(TH, S::NT * S::MAXX / t.NQ - 2 * PH);              // x prefetch registers
     }
-    TH = min(TH, H);
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
         return (size_t)FwdSmem<KD, KH, KW>(q).total_floats * sizeof(float);
     };
-    while (TH > 1 && bytes(TH) > kSmemTwoPerSM) --TH;
-    if (TH < 1 || bytes(TH) > kSmemMax) return false;
+    while (TH > 1 && (bytes(TH) > kSmemTwoPerSM || SCH * (TH + 4 * PH) * t.pitch > 65535)) --TH;
+    if (TH < 1 || bytes(TH) > kSmemMax || SCH * (TH + 4 * PH) * t.pitch > 65535) return false;
     t.nth = (H + TH - 1) / TH;
     t.TH = (H + t.nth - 1) / t.nth;
-    if (KD == 1) {
-        t.DC = 1;
-    } else {
-        const long long target = 6LL * 2 * kNumSMs;  // about six waves of two CTAs per SM
-        long long ndc = target / max(1LL, BC * t.nth);
-        ndc = max(1LL, min(ndc, (long long)max(1, D / 8)));
-        t.DC = (int)((D + ndc - 1) / ndc);
-    }
-    t.ndc = (D + t.DC - 1) / t.DC;
+    plan_depth(KD, D, BC * t.nth, 5, t);
     smem_bytes = bytes(t.TH);
     return true;
 }
@@ -64,7 +72,7 @@ inline bool aligned_for_vec(const void* p, int dtype) {
 template <typename T, int KD, int KH, int KW, bool VEC>
 cudaError_t launch_fwd(const FwdParams& P, size_t smem_bytes, long long BC, cudaStream_t st) {
     using S = FwdShape<KD, KH, KW>;
-    auto kern = fwd_kernel<T, KD, KH, KW, S::NT, S::RK, S::RA, S::MAXZ, S::MAXX, S::MINB, VEC>;
+    auto kern = fwd_kernel<T, KD, KH, KW, S::NT, S::MAXZ, S::MAXX, S::MINB, VEC>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem_bytes);
     if (e != cudaSuccess) return e;
@@ -88,7 +96,6 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
     P.eps = g.eps; P.relu = g.relu;
     const bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
                      aligned_for_vec(out, dtype) && aligned_for_vec(t1, dtype);
-    P.t.vec = vec;
     return vec ? launch_fwd<T, KD, KH, KW, true>(P, smem, BC, st)
                : launch_fwd<T, KD, KH, KW, false>(P, smem, BC, st);
 }
