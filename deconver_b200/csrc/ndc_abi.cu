@@ -137,6 +137,10 @@ int ndc_fwd(const NdcDesc* desc, const void* x, const void* z, const float* h, c
 size_t ndc_bwd_workspace_bytes(const NdcDesc* desc) {
     if (validate(desc) != NDC_OK) return 0;
     const ndc::Geo g = ndc::make_geo(*desc, false);
+    if (path_of(desc) == NDC_PATH_DEPTHWISE4) {
+        ndc::dw4::BwdPlan p;
+        if (ndc::dw4::plan_bwd_any(g, p)) return p.bytes;
+    }
     return ndc::generic::bwd_scratch(g).bytes;
 }
 
@@ -165,6 +169,23 @@ int ndc_bwd(const NdcDesc* desc, const void* x, const void* z, const void* t1, c
     const ndc::Geo g = ndc::make_geo(*desc, bias != nullptr);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
+    if (path_of(desc) == NDC_PATH_DEPTHWISE4) {
+        ndc::dw4::BwdPlan p;
+        if (ndc::dw4::plan_bwd_any(g, p)) {
+            typedef __nv_bfloat16 bf16;
+            if (desc->dtype == NDC_F32)
+                e = ndc::dw4::backward<float>(g, p, (const float*)x, (const float*)z,
+                                              (const float*)t1, h, bias, (const float*)gout,
+                                              (float*)gx, (float*)gz, gh, gb, workspace,
+                                              desc->dtype, st);
+            else
+                e = ndc::dw4::backward<bf16>(g, p, (const bf16*)x, (const bf16*)z, (const bf16*)t1,
+                                             h, bias, (const bf16*)gout, (bf16*)gx, (bf16*)gz, gh,
+                                             gb, workspace, desc->dtype, st);
+            if (e != cudaSuccess) return cuda_fail(e, "ndc_bwd (depthwise) launch");
+            return NDC_OK;
+        }
+    }
     if (desc->dtype == NDC_F32)
         e = ndc::generic::backward<float>(g, (const float*)x, (const float*)z, (const float*)t1, h,
                                           bias, (const float*)gout, (float*)gx, (float*)gz, gh, gb,

@@ -1,0 +1,663 @@
+// Backward of the update for the depthwise ratio-4 geometry (m = 1, sc = 4), four kernels:
+//
+//   ratio_kernel    per voxel: n = A(x)+eps, d = A(t1)+eps recomputed from shared-memory rings,
+//                   gnum = g*s/d, gden = -(gnum*n)/d (float32 scratch), the direct term
+//                   (g*n)/d (into the gz buffer), and two of the three filter-gradient
+//                   correlations:  sum_p gden[j,p] t1[p+pad-tau] + gnum[j,p] x[p+pad-tau]
+//   kconv_kernel    K applied to a 4-channel float32 tensor with running sums along depth:
+//                   gt1 = K(gden) (scratch) and gx = K(gnum)
+//   gz_kernel       gz = [z+b>0] * (direct + A(gt1)) in place, gb = sum gz, and the third
+//                   correlation  sum_p s[j,p] gt1[p+pad-tau]
+//   reduce_kernel   fixed-order sum of the per-CTA partial filter/bias gradients
+//
+// The correlations are accumulated in 27*4 (or 25*4, 9*4) registers per thread over all the
+// strips a thread visits, then combined per CTA in a fixed order: no atomics anywhere, so the
+// gradients are bitwise reproducible.
+#pragma once
+
+#include "ndc_dw4_common.cuh"
+
+namespace ndc {
+namespace dw4 {
+
+constexpr int kPartialStride = 128;  // floats per CTA partial record (taps*4 + 4 bias sums, padded)
+
+// ------------------------------------------------------------------------------------------
+// Rings of single-channel planes, shifted layout, read by 4-voxel strips.
+template <int KD, int KH, int KW>
+struct RingSmem {
+    static constexpr int PD = KD / 2, PH = KH / 2;
+    static constexpr int RING = KD > 1 ? KD + 1 : 1;
+    int wA, ring0, desc, total_floats, RT, plane_t;
+    __host__ __device__ RingSmem(const Tiling& t, int ntensors, int nthreads) {
+        RT = t.TH + 2 * PH;
+        plane_t = RT * t.pitch;
+        int o = 0;
+        wA = o; o += KD * KH * KW * SCH;
+        o = (o + 3) / 4 * 4;
+        ring0 = o; o += ntensors * RING * plane_t;
+        desc = o; o += KD > 1 ? 2 * (RT * t.NQ) : 0;
+        // the end-of-kernel reduction reuses the ring area: nthreads rows of (taps*4 + 5) floats
+        const int red = nthreads * (KD * KH * KW * SCH + 5);
+        if (o - ring0 < red) o = ring0 + red;
+        total_floats = o;
+    }
+};
+
+struct RatioParams {
+    const void* x; const void* t1; const void* z; const void* gout;
+    const float* h; const float* bias;
+    float* gnum; float* gden;   // float32 scratch, source-sized
+    void* gz;                   // direct term goes here (storage dtype), or NULL
+    float* partial;             // [cta][kPartialStride], or NULL
+    int C, D, H, W;
+    Tiling t;
+    float eps;
+    int relu;
+};
+
+// Deterministic per-CTA combine of per-thread accumulators: every thread writes its NACC values
+// to a padded row of shared memory, then thread k sums column k over the threads in order.
+template <int NACC, int NT>
+__device__ __forceinline__ void cta_combine(float* scratch, const float (&acc)[NACC], float* out) {
+    constexpr int LD = NACC + 1;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < NACC; ++k) scratch[threadIdx.x * LD + k] = acc[k];
+    __syncthreads();
+    for (int k = threadIdx.x; k < NACC; k += NT) {
+        float s = 0.0f;
+        for (int i = 0; i < NT; ++i) s += scratch[i * LD + k];
+        out[k] = s;
+    }
+}
+
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD>
+__global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
+    constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
+    using L = RingSmem<KD, KH, KW>;
+    constexpr int RING = L::RING;
+    constexpr int NQA = 1 + (2 * PW + 3) / 4;
+    extern __shared__ __align__(16) float smem[];
+    const L lay(P.t, 2, NT);
+    const int tid = threadIdx.x;
+    const int NQ = P.t.NQ, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const long long HW = (long long)H * W, SP = HW * D;
+
+    int blk = blockIdx.x;
+    const int th = blk % P.t.nth; blk /= P.t.nth;
+    const int dch = blk % P.t.ndc; blk /= P.t.ndc;
+    const int bc = blk;
+    const int c = bc % P.C;
+    const int h0 = th * P.t.TH;
+    const int TH = min(P.t.TH, H - h0);
+    const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
+    const int RT = lay.RT;
+
+    const T* xg = reinterpret_cast<const T*>(P.x) + (long long)bc * SP;
+    const T* tg = reinterpret_cast<const T*>(P.t1) + (long long)bc * SP;
+    const T* zg = reinterpret_cast<const T*>(P.z) + (long long)bc * SCH * SP;
+    const T* gg = reinterpret_cast<const T*>(P.gout) + (long long)bc * SCH * SP;
+    float* gng = P.gnum + (long long)bc * SCH * SP;
+    float* gdg = P.gden + (long long)bc * SCH * SP;
+    T* dirg = P.gz ? reinterpret_cast<T*>(P.gz) + (long long)bc * SCH * SP : nullptr;
+
+    float* wA = smem + lay.wA;
+    float* xring = smem + lay.ring0;
+    float* tring = xring + RING * lay.plane_t;
+    ChunkDesc* desc = reinterpret_cast<ChunkDesc*>(smem + lay.desc);
+
+    for (int i = tid; i < 2 * RING * lay.plane_t; i += NT) xring[i] = 0.0f;
+    {
+        const float* hc = P.h + (long long)c * SCH * KT;
+        for (int i = tid; i < KT * SCH; i += NT) wA[i] = hc[(i % SCH) * KT + i / SCH];  // [tau][j]
+    }
+    const int nx = RT * NQ;
+    if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
+    float bj[SCH];
+#pragma unroll
+    for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
+    float accw[WGRAD ? KT * SCH : 1];
+#pragma unroll
+    for (int k = 0; k < (WGRAD ? KT * SCH : 1); ++k) accw[k] = 0.0f;
+    __syncthreads();
+
+    const int qbase = d0 - PD - 1;
+    auto slot_of = [&](int q) { return (q - qbase) % RING; };
+    auto load_now = [&](const T* src_t, float* ring, int plane) {
+        const T* src = src_t + (long long)plane * HW;
+        float* dst = ring + slot_of(plane) * lay.plane_t;
+        for (int id = tid; id < nx; id += NT) {
+            const int c4 = id % NQ, r = id / NQ;
+            const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
+            if (h < 0 || h >= H) continue;
+            stage_chunk<PW, false>(dst, (r * pitch) | (w << 16) | (n << 26),
+                                   load4<T, VEC>(src + (long long)h * W + w, n));
+        }
+    };
+    // prologue: planes d0-PD .. d0+PD
+    for (int q = d0 - PD; q <= d0 + PD; ++q)
+        if (q >= 0 && q < D) { load_now(xg, xring, q); load_now(tg, tring, q); }
+    __syncthreads();
+
+    const int items = TH * NQ;
+    for (int d = d0; d < d1; ++d) {
+        // prefetch the plane the next step needs
+        float4 xr[MAXX], tr[MAXX];
+        const int qn = d + PD + 1;
+        const bool have = KD > 1 && d + 1 < d1 && qn < D;
+        if (have) {
+#pragma unroll
+            for (int i = 0; i < MAXX; ++i) {
+                const int id = tid + i * NT;
+                if (id < nx) {
+                    const ChunkDesc dsc = desc[id];
+                    if (dsc.goff >= 0) {
+                        xr[i] = load4<T, VEC>(xg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
+                        tr[i] = load4<T, VEC>(tg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
+                    }
+                }
+            }
+        }
+#pragma unroll 1
+        for (int item = tid; item < items; item += NT) {
+            const int a_row = item / NQ, a_q = item % NQ;
+            const int hrow = h0 + a_row, w0 = VA * a_q;
+            const long long off = (long long)d * HW + (long long)hrow * W;
+            float an[SCH][VA], ad[SCH][VA];
+#pragma unroll
+            for (int j = 0; j < SCH; ++j)
+#pragma unroll
+                for (int v = 0; v < VA; ++v) { an[j][v] = P.eps; ad[j][v] = P.eps; }
+#pragma unroll 1
+            for (int kd = 0; kd < KD; ++kd) {
+                const int q = d + PD - kd;
+                if (q < 0 || q >= D) continue;
+                const int slot = slot_of(q);
+#pragma unroll
+                for (int kh = 0; kh < KH; ++kh) {
+                    const int rr = a_row + PH + PH - kh;
+                    float xv[4 * NQA], tv[4 * NQA];
+                    load_window<NQA, false>(xring + slot * lay.plane_t + rr * pitch, a_q + 1, xv);
+                    load_window<NQA, false>(tring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
+#pragma unroll
+                    for (int kw = 0; kw < KW; ++kw) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(
+                            wA + ((kd * KH + kh) * KW + kw) * SCH);
+                        const float wj[SCH] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (int j = 0; j < SCH; ++j)
+#pragma unroll
+                            for (int v = 0; v < VA; ++v) {
+                                an[j][v] = fmaf(xv[v + 2 * PW - kw], wj[j], an[j][v]);
+                                ad[j][v] = fmaf(tv[v + 2 * PW - kw], wj[j], ad[j][v]);
+                            }
+                    }
+                }
+            }
+            // epilogue: gnum, gden, direct term (an/ad are overwritten with gnum/gden)
+#pragma unroll
+            for (int j = 0; j < SCH; ++j) {
+                float zv[VA], gv[VA], dv[VA];
+                load_strip_global<T, VEC, VA>(zg + j * SP + off, w0, W, zv);
+                load_strip_global<T, VEC, VA>(gg + j * SP + off, w0, W, gv);
+#pragma unroll
+                for (int v = 0; v < VA; ++v) {
+                    float s = zv[v] + bj[j];
+                    if (P.relu) s = fmaxf(s, 0.0f);
+                    const float r = fast_div(1.0f, ad[j][v]);
+                    const float gr = gv[v] * r;
+                    const float gn = gr * s;
+                    dv[v] = gr * an[j][v];
+                    ad[j][v] = -(gn * an[j][v]) * r;
+                    an[j][v] = gn;
+                    if (w0 + v >= W) { an[j][v] = 0.0f; ad[j][v] = 0.0f; }
+                }
+                store_strip_global<float, VEC, VA>(gng + j * SP + off, w0, W, an[j]);
+                store_strip_global<float, VEC, VA>(gdg + j * SP + off, w0, W, ad[j]);
+                if (dirg) store_strip_global<T, VEC, VA>(dirg + j * SP + off, w0, W, dv);
+            }
+            if (WGRAD) {
+#pragma unroll
+                for (int kd = 0; kd < KD; ++kd) {
+                    const int q = d + PD - kd;
+                    if (q < 0 || q >= D) continue;
+                    const int slot = slot_of(q);
+#pragma unroll
+                    for (int kh = 0; kh < KH; ++kh) {
+                        const int rr = a_row + PH + PH - kh;
+                        float xv[4 * NQA], tv[4 * NQA];
+                        load_window<NQA, false>(xring + slot * lay.plane_t + rr * pitch, a_q + 1, xv);
+                        load_window<NQA, false>(tring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
+#pragma unroll
+                        for (int kw = 0; kw < KW; ++kw)
+#pragma unroll
+                            for (int j = 0; j < SCH; ++j) {
+                                float a = accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0];
+#pragma unroll
+                                for (int v = 0; v < VA; ++v) {
+                                    a = fmaf(ad[j][v], tv[v + 2 * PW - kw], a);
+                                    a = fmaf(an[j][v], xv[v + 2 * PW - kw], a);
+                                }
+                                accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] = a;
+                            }
+                    }
+                }
+            }
+        }
+        if (have) {
+#pragma unroll
+            for (int i = 0; i < MAXX; ++i) {
+                const int id = tid + i * NT;
+                if (id < nx) {
+                    const ChunkDesc dsc = desc[id];
+                    if (dsc.goff >= 0) {
+                        stage_chunk<PW, false>(xring + slot_of(qn) * lay.plane_t, dsc.soff, xr[i]);
+                        stage_chunk<PW, false>(tring + slot_of(qn) * lay.plane_t, dsc.soff, tr[i]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (WGRAD && P.partial)
+        cta_combine<WGRAD ? KT * SCH : 1, NT>(xring, accw, P.partial + (long long)blockIdx.x * kPartialStride);
+}
+
+// ------------------------------------------------------------------------------------------
+// K applied to a 4-channel float32 tensor (gnum or gden) with running sums along depth.
+struct KconvParams {
+    const float* in[2];     // gridDim.y selects: [0] gden -> gt1 (float32), [1] gnum -> gx (T)
+    void* out[2];
+    int out_is_f32[2];
+    const float* h;
+    int C, D, H, W;
+    Tiling t;
+};
+
+template <int KD, int KH, int KW>
+struct KconvSmem {
+    static constexpr int PD = KD / 2, PH = KH / 2;
+    static constexpr int WKP = (KD * KW + 3) / 4 * 4;
+    static constexpr int NSB = KD > 1 ? 2 : 1;
+    int wK, sbuf, desc, total_floats, RS, plane_s;
+    __host__ __device__ KconvSmem(const Tiling& t) {
+        RS = t.TH + 2 * PH;
+        plane_s = SCH * RS * t.pitch;
+        int o = 0;
+        wK = o; o += KH * SCH * WKP;
+        o = (o + 3) / 4 * 4;
+        sbuf = o; o += NSB * plane_s;
+        desc = o; o += KD > 1 ? 2 * (SCH * RS * t.NQ) : 0;
+        total_floats = o;
+    }
+};
+
+template <typename T, int KD, int KH, int KW, int NT, int MAXZ, bool VEC>
+__global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
+    constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
+    using L = KconvSmem<KD, KH, KW>;
+    constexpr int WKP = L::WKP, NSB = L::NSB;
+    constexpr int NQK = 2 + (2 * PW + 3) / 4;
+    extern __shared__ __align__(16) float smem[];
+    const L lay(P.t);
+    const int tid = threadIdx.x;
+    const int NQ = P.t.NQ, NS8 = (NQ + 1) / 2, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const long long HW = (long long)H * W, SP = HW * D;
+    const int which = blockIdx.y;
+
+    int blk = blockIdx.x;
+    const int th = blk % P.t.nth; blk /= P.t.nth;
+    const int dch = blk % P.t.ndc; blk /= P.t.ndc;
+    const int bc = blk;
+    const int c = bc % P.C;
+    const int h0 = th * P.t.TH;
+    const int TH = min(P.t.TH, H - h0);
+    const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
+    const int RS = lay.RS;
+
+    const float* ing = P.in[which] + (long long)bc * SCH * SP;
+    float* outf = P.out_is_f32[which] ? reinterpret_cast<float*>(P.out[which]) + (long long)bc * SP : nullptr;
+    T* outt = P.out_is_f32[which] ? nullptr : reinterpret_cast<T*>(P.out[which]) + (long long)bc * SP;
+
+    float* wK = smem + lay.wK;
+    float* sbuf = smem + lay.sbuf;
+    ChunkDesc* desc = reinterpret_cast<ChunkDesc*>(smem + lay.desc);
+    for (int i = tid; i < NSB * lay.plane_s; i += NT) sbuf[i] = 0.0f;
+    {
+        const float* hc = P.h + (long long)c * SCH * (KD * KH * KW);
+        for (int i = tid; i < KH * SCH * WKP; i += NT) {
+            const int e = i % WKP, j = (i / WKP) % SCH, kh = i / (WKP * SCH);
+            float v = 0.0f;
+            if (e < KD * KW) v = hc[j * (KD * KH * KW) + ((e / KW) * KH + kh) * KW + e % KW];
+            wK[i] = v;
+        }
+    }
+    const int nz = SCH * RS * NQ;
+    if (KD > 1) build_descs(desc, SCH, RS, NQ, pitch, h0 - PH, H, W, SP, NT);
+    const int k_row = tid / NS8, k_strip = tid % NS8;   // row of the output band (no halo rows)
+    const bool k_ok = tid < TH * NS8;
+    float kacc[KD][VK];
+#pragma unroll
+    for (int a = 0; a < KD; ++a)
+#pragma unroll
+        for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
+    __syncthreads();
+
+    auto load_now = [&](int plane) {
+        const float* src = ing + (long long)plane * HW;
+        float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
+        for (int id = tid; id < nz; id += NT) {
+            const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
+            const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
+            if (h < 0 || h >= H) continue;
+            stage_chunk<PW, true>(dst, ((ch * RS + r) * pitch) | (w << 16) | (n << 26),
+                                  load4<float, VEC>(src + ch * SP + (long long)h * W + w, n));
+        }
+    };
+    const int p_first = d0 - PD, p_last = d1 - 1 + PD;
+    if (p_first >= 0 && p_first < D) load_now(p_first);
+    __syncthreads();
+
+    for (int p = p_first; p <= p_last; ++p) {
+        float4 zr[MAXZ];
+        const bool have = KD > 1 && p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
+        if (have) {
+#pragma unroll
+            for (int i = 0; i < MAXZ; ++i) {
+                const int id = tid + i * NT;
+                if (id < nz) {
+                    const ChunkDesc dsc = desc[id];
+                    if (dsc.goff >= 0)
+                        zr[i] = load4<float, VEC>(ing + (long long)(p + 1) * HW + dsc.goff, desc_n(dsc.soff));
+                }
+            }
+        }
+        const bool s_ok = p >= 0 && p < D;
+        const int qdone = p - PD;
+        const bool q_need = qdone >= d0 && qdone < d1;
+        auto accumulate = [&](int row, int strip, float (&acc)[KD][VK]) {
+            const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + row * pitch;
+#pragma unroll 1
+            for (int kh = 0; kh < KH; ++kh) {
+#pragma unroll 1
+                for (int j = 0; j < SCH; ++j) {
+                    float sv[4 * NQK];
+                    load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
+                    float w[WKP];
+#pragma unroll
+                    for (int q4 = 0; q4 < WKP / 4; ++q4) {
+                        const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + j) * WKP + 4 * q4);
+                        w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
+                    }
+#pragma unroll
+                    for (int kd = 0; kd < KD; ++kd)
+#pragma unroll
+                        for (int kw = 0; kw < KW; ++kw)
+#pragma unroll
+                            for (int v = 0; v < VK; ++v)
+                                acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
+                }
+            }
+        };
+        auto finish = [&](int row, int strip, const float (&done)[VK]) {
+            const long long off = (long long)qdone * HW + (long long)(h0 + row) * W;
+            if (outf) store_strip_global<float, VEC, VK>(outf + off, VK * strip, W, done);
+            else store_strip_global<T, VEC, VK>(outt + off, VK * strip, W, done);
+        };
+        if (KD > 1) {
+            if (k_ok) {
+                if (s_ok) accumulate(k_row, k_strip, kacc);
+                if (q_need) finish(k_row, k_strip, kacc[KD - 1]);
+            }
+#pragma unroll
+            for (int kd = KD - 1; kd > 0; --kd)
+#pragma unroll
+                for (int v = 0; v < VK; ++v) kacc[kd][v] = kacc[kd - 1][v];
+#pragma unroll
+            for (int v = 0; v < VK; ++v) kacc[0][v] = 0.0f;
+        } else if (s_ok && q_need) {
+#pragma unroll 1
+            for (int item = tid; item < TH * NS8; item += NT) {
+                float acc[KD][VK];
+#pragma unroll
+                for (int v = 0; v < VK; ++v) acc[0][v] = 0.0f;
+                accumulate(item / NS8, item % NS8, acc);
+                finish(item / NS8, item % NS8, acc[KD - 1]);
+            }
+        }
+        if (have) {
+            float* dst = sbuf + ((p + 1) & (NSB - 1)) * lay.plane_s;
+#pragma unroll
+            for (int i = 0; i < MAXZ; ++i) {
+                const int id = tid + i * NT;
+                if (id < nz) {
+                    const ChunkDesc dsc = desc[id];
+                    if (dsc.goff >= 0) stage_chunk<PW, true>(dst, dsc.soff, zr[i]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+struct GzParams {
+    const float* gt1;           // float32 scratch
+    const void* z;
+    void* gz;                   // holds the direct term on entry, gz on exit (or NULL)
+    const float* h; const float* bias;
+    float* partial;             // [cta][kPartialStride]
+    int C, D, H, W;
+    Tiling t;
+    int relu;
+};
+
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD>
+__global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
+    constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
+    using L = RingSmem<KD, KH, KW>;
+    constexpr int RING = L::RING;
+    constexpr int NQA = 1 + (2 * PW + 3) / 4;
+    constexpr int NACC = (WGRAD ? KT * SCH : 0) + SCH;
+    extern __shared__ __align__(16) float smem[];
+    const L lay(P.t, 1, NT);
+    const int tid = threadIdx.x;
+    const int NQ = P.t.NQ, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const long long HW = (long long)H * W, SP = HW * D;
+
+    int blk = blockIdx.x;
+    const int th = blk % P.t.nth; blk /= P.t.nth;
+    const int dch = blk % P.t.ndc; blk /= P.t.ndc;
+    const int bc = blk;
+    const int c = bc % P.C;
+    const int h0 = th * P.t.TH;
+    const int TH = min(P.t.TH, H - h0);
+    const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
+    const int RT = lay.RT;
+
+    const float* tg = P.gt1 + (long long)bc * SP;
+    const T* zg = reinterpret_cast<const T*>(P.z) + (long long)bc * SCH * SP;
+    T* gzg = P.gz ? reinterpret_cast<T*>(P.gz) + (long long)bc * SCH * SP : nullptr;
+
+    float* wA = smem + lay.wA;
+    float* ring = smem + lay.ring0;
+    ChunkDesc* desc = reinterpret_cast<ChunkDesc*>(smem + lay.desc);
+    for (int i = tid; i < RING * lay.plane_t; i += NT) ring[i] = 0.0f;
+    {
+        const float* hc = P.h + (long long)c * SCH * KT;
+        for (int i = tid; i < KT * SCH; i += NT) wA[i] = hc[(i % SCH) * KT + i / SCH];
+    }
+    const int nx = RT * NQ;
+    if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
+    float bj[SCH];
+#pragma unroll
+    for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
+    float acc[NACC];   // [taps*4] filter-gradient sums (if WGRAD), then 4 bias sums
+#pragma unroll
+    for (int k = 0; k < NACC; ++k) acc[k] = 0.0f;
+    __syncthreads();
+
+    const int qbase = d0 - PD - 1;
+    auto slot_of = [&](int q) { return (q - qbase) % RING; };
+    auto load_now = [&](int plane) {
+        const float* src = tg + (long long)plane * HW;
+        float* dst = ring + slot_of(plane) * lay.plane_t;
+        for (int id = tid; id < nx; id += NT) {
+            const int c4 = id % NQ, r = id / NQ;
+            const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
+            if (h < 0 || h >= H) continue;
+            stage_chunk<PW, false>(dst, (r * pitch) | (w << 16) | (n << 26),
+                                   load4<float, VEC>(src + (long long)h * W + w, n));
+        }
+    };
+    for (int q = d0 - PD; q <= d0 + PD; ++q)
+        if (q >= 0 && q < D) load_now(q);
+    __syncthreads();
+
+    const int items = TH * NQ;
+    for (int d = d0; d < d1; ++d) {
+        float4 tr[MAXX];
+        const int qn = d + PD + 1;
+        const bool have = KD > 1 && d + 1 < d1 && qn < D;
+        if (have) {
+#pragma unroll
+            for (int i = 0; i < MAXX; ++i) {
+                const int id = tid + i * NT;
+                if (id < nx) {
+                    const ChunkDesc dsc = desc[id];
+                    if (dsc.goff >= 0)
+                        tr[i] = load4<float, VEC>(tg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
+                }
+            }
+        }
+#pragma unroll 1
+        for (int item = tid; item < items; item += NT) {
+            const int a_row = item / NQ, a_q = item % NQ;
+            const int hrow = h0 + a_row, w0 = VA * a_q;
+            const long long off = (long long)d * HW + (long long)hrow * W;
+            float sv[SCH][VA], pre[SCH][VA];
+#pragma unroll
+            for (int j = 0; j < SCH; ++j) {
+                load_strip_global<T, VEC, VA>(zg + j * SP + off, w0, W, pre[j]);
+#pragma unroll
+                for (int v = 0; v < VA; ++v) {
+                    pre[j][v] += bj[j];
+                    sv[j][v] = P.relu ? fmaxf(pre[j][v], 0.0f) : pre[j][v];
+                    if (w0 + v >= W) sv[j][v] = 0.0f;
+                }
+            }
+            float ag[SCH][VA];
+#pragma unroll
+            for (int j = 0; j < SCH; ++j)
+#pragma unroll
+                for (int v = 0; v < VA; ++v) ag[j][v] = 0.0f;
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd) {
+                const int q = d + PD - kd;
+                if (q < 0 || q >= D) continue;
+                const int slot = slot_of(q);
+#pragma unroll
+                for (int kh = 0; kh < KH; ++kh) {
+                    const int rr = a_row + PH + PH - kh;
+                    float tv[4 * NQA];
+                    load_window<NQA, false>(ring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
+#pragma unroll
+                    for (int kw = 0; kw < KW; ++kw) {
+                        const float4 w4 = *reinterpret_cast<const float4*>(
+                            wA + ((kd * KH + kh) * KW + kw) * SCH);
+                        const float wj[SCH] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (int j = 0; j < SCH; ++j) {
+                            float a = WGRAD ? acc[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] : 0.0f;
+#pragma unroll
+                            for (int v = 0; v < VA; ++v) {
+                                ag[j][v] = fmaf(tv[v + 2 * PW - kw], wj[j], ag[j][v]);
+                                if (WGRAD) a = fmaf(sv[j][v], tv[v + 2 * PW - kw], a);
+                            }
+                            if (WGRAD) acc[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] = a;
+                        }
+                    }
+                }
+            }
+            if (gzg) {
+#pragma unroll
+                for (int j = 0; j < SCH; ++j) {
+                    float dv[VA];
+                    load_strip_global<T, VEC, VA>(gzg + j * SP + off, w0, W, dv);
+#pragma unroll
+                    for (int v = 0; v < VA; ++v) {
+                        float r = dv[v] + ag[j][v];
+                        if (P.relu && !(pre[j][v] > 0.0f)) r = 0.0f;
+                        if (w0 + v >= W) r = 0.0f;
+                        dv[v] = r;
+                        // the bias gradient sums the values as stored (rounded to the storage type)
+                        acc[NACC - SCH + j] += to_f32(from_f32<T>(r));
+                    }
+                    store_strip_global<T, VEC, VA>(gzg + j * SP + off, w0, W, dv);
+                }
+            }
+        }
+        if (have) {
+#pragma unroll
+            for (int i = 0; i < MAXX; ++i) {
+                const int id = tid + i * NT;
+                if (id < nx) {
+                    const ChunkDesc dsc = desc[id];
+                    if (dsc.goff >= 0) stage_chunk<PW, false>(ring + slot_of(qn) * lay.plane_t, dsc.soff, tr[i]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    float* out = P.partial + (long long)blockIdx.x * kPartialStride;
+    // record layout: [0, taps*4) filter sums (zero if not WGRAD), [124, 128) bias sums
+    constexpr int LD = NACC + 1;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < NACC; ++k) ring[tid * LD + k] = acc[k];
+    __syncthreads();
+    for (int k = tid; k < NACC; k += NT) {
+        float s = 0.0f;
+        for (int i = 0; i < NT; ++i) s += ring[i * LD + k];
+        const bool is_bias = k >= NACC - SCH;
+        out[is_bias ? kPartialStride - SCH + (k - (NACC - SCH)) : k] = s;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// gh[c][j][tau] = sum over CTAs of group c, in launch order, of both partial sets; gb likewise.
+struct ReduceParams {
+    const float* partial_a;   // ratio kernel records (or NULL)
+    const float* partial_b;   // gz kernel records (or NULL)
+    long long ctas_per_bc_a, ctas_per_bc_b;  // records per (sample, group) pair
+    int b_has_w;              // the gz records carry filter sums
+    int B, C, KT;
+    float* gh;    // (C, 4, KT) or NULL
+    float* gb;    // (C*4) or NULL
+};
+
+__global__ void __launch_bounds__(128) reduce_kernel(const ReduceParams P) {
+    const int c = blockIdx.x;
+    const int k = threadIdx.x;       // record slot
+    const bool is_w = k < P.KT * SCH, is_b = k >= kPartialStride - SCH;
+    if (!is_w && !is_b) return;
+    float s = 0.0f;
+    for (int b = 0; b < P.B; ++b) {
+        const long long bc = (long long)b * P.C + c;
+        if (P.partial_a && is_w)
+            for (long long i = 0; i < P.ctas_per_bc_a; ++i)
+                s += P.partial_a[(bc * P.ctas_per_bc_a + i) * kPartialStride + k];
+        if (P.partial_b && (is_b || P.b_has_w))
+            for (long long i = 0; i < P.ctas_per_bc_b; ++i)
+                s += P.partial_b[(bc * P.ctas_per_bc_b + i) * kPartialStride + k];
+    }
+    if (is_w && P.gh) {
+        const int j = k % SCH, tau = k / SCH;     // records are [tau][j]; gh is (c, j, tau)
+        P.gh[((long long)c * SCH + j) * P.KT + tau] = s;
+    }
+    if (is_b && P.gb) P.gb[c * SCH + (k - (kPartialStride - SCH))] = s;
+}
+
+}  // namespace dw4
+}  // namespace ndc

@@ -4,6 +4,7 @@
 #include <algorithm>
 
 #include "ndc_dw4_fwd.cuh"
+#include "ndc_dw4_bwd.cuh"
 
 namespace ndc {
 namespace dw4 {
@@ -100,11 +101,206 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
                : launch_fwd<T, KD, KH, KW, false>(P, smem, BC, st);
 }
 
+// ---------------------------------------------------------------------------- backward
+
+constexpr int kRingNT = 128;    // ratio_kernel / gz_kernel threads
+constexpr int kRingMAXX = 4;    // prefetch registers (quads) per tensor
+constexpr int kKconvNT = 128;
+constexpr int kKconvMAXZ = 10;
+
+// Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
+template <int KD, int KH, int KW>
+inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, Tiling& t, size_t& smem_bytes) {
+    constexpr int PH = KH / 2;
+    if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
+    t.NQ = (W + 3) / 4;
+    t.pitch = row_pitch(W);
+    int TH = H;
+    if (KD > 1) TH = std::min(TH, kRingNT * kRingMAXX / t.NQ - 2 * PH);
+    auto bytes = [&](int th) {
+        Tiling q = t; q.TH = th;
+        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, kRingNT).total_floats * sizeof(float);
+    };
+    while (TH > 1 && (bytes(TH) > kSmemTwoPerSM || (TH + 2 * PH) * t.pitch > 65535)) --TH;
+    if (TH < 1 || bytes(TH) > kSmemMax) return false;
+    t.nth = (H + TH - 1) / TH;
+    t.TH = (H + t.nth - 1) / t.nth;
+    plan_depth(KD, D, BC * t.nth, 6, t);
+    smem_bytes = bytes(t.TH);
+    return true;
+}
+
+template <int KD, int KH, int KW>
+inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
+    constexpr int PH = KH / 2;
+    if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
+    t.NQ = (W + 3) / 4;
+    t.pitch = row_pitch(W);
+    const int NS8 = (t.NQ + 1) / 2;
+    int TH = H;
+    if (KD > 1) {
+        TH = std::min(TH, kKconvNT / NS8);
+        TH = std::min(TH, kKconvNT * kKconvMAXZ / (SCH * t.NQ) - 2 * PH);
+    }
+    auto bytes = [&](int th) {
+        Tiling q = t; q.TH = th;
+        return (size_t)KconvSmem<KD, KH, KW>(q).total_floats * sizeof(float);
+    };
+    while (TH > 1 && (bytes(TH) > 72 * 1024 || SCH * (TH + 2 * PH) * t.pitch > 65535)) --TH;
+    if (TH < 1 || bytes(TH) > kSmemMax) return false;
+    t.nth = (H + TH - 1) / TH;
+    t.TH = (H + t.nth - 1) / t.nth;
+    plan_depth(KD, D, 2 * BC * t.nth, 6, t);
+    smem_bytes = bytes(t.TH);
+    return true;
+}
+
+struct BwdPlan {
+    Tiling ratio, kconv, gz;
+    size_t smem_ratio, smem_kconv, smem_gz;
+    size_t off_gnum, off_gden, off_gt1, off_pa, off_pb, bytes;
+    long long n_ratio, n_gz;   // CTAs (= partial records)
+};
+
+template <int KD, int KH, int KW>
+inline bool plan_bwd(const Geo& g, BwdPlan& p) {
+    const long long BC = (long long)g.B * g.G;
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, p.ratio, p.smem_ratio)) return false;
+    if (!plan_kconv<KD, KH, KW>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, p.gz, p.smem_gz)) return false;
+    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    const size_t src = (size_t)BC * SCH * g.SP * sizeof(float);
+    const size_t flt = (size_t)BC * g.SP * sizeof(float);
+    p.n_ratio = BC * p.ratio.ndc * p.ratio.nth;
+    p.n_gz = BC * p.gz.ndc * p.gz.nth;
+    p.off_gnum = 0;
+    p.off_gden = up(src);
+    p.off_gt1 = p.off_gden + up(src);
+    p.off_pa = p.off_gt1 + up(flt);
+    p.off_pb = p.off_pa + up((size_t)p.n_ratio * kPartialStride * sizeof(float));
+    p.bytes = p.off_pb + up((size_t)p.n_gz * kPartialStride * sizeof(float));
+    return true;
+}
+
+inline bool plan_bwd_any(const Geo& g, BwdPlan& p) {
+    if (g.m != 1 || g.sc != SCH) return false;
+    if (g.kD == 3 && g.kH == 3 && g.kW == 3) return plan_bwd<3, 3, 3>(g, p);
+    if (g.kD == 1 && g.kH == 5 && g.kW == 5) return plan_bwd<1, 5, 5>(g, p);
+    if (g.kD == 1 && g.kH == 3 && g.kW == 3) return plan_bwd<1, 3, 3>(g, p);
+    return false;
+}
+
+template <typename K>
+inline cudaError_t set_smem(K kern, size_t bytes) {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+#define NDC_CUDA_TRY(expr)                      \
+    do {                                        \
+        cudaError_t _e = (expr);                \
+        if (_e != cudaSuccess) return _e;       \
+    } while (0)
+
+template <typename T, int KD, int KH, int KW, bool VEC>
+cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
+                            const float* h, const float* bias, const T* gout, T* gx, T* gz,
+                            float* gh, float* gb, void* ws, cudaStream_t st) {
+    const long long BC = (long long)g.B * g.G;
+    float* gnum = (float*)((char*)ws + p.off_gnum);
+    float* gden = (float*)((char*)ws + p.off_gden);
+    float* gt1 = (float*)((char*)ws + p.off_gt1);
+    float* pa = (float*)((char*)ws + p.off_pa);
+    float* pb = (float*)((char*)ws + p.off_pb);
+    {
+        RatioParams P;
+        P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;
+        P.gnum = gnum; P.gden = gden; P.gz = gz; P.partial = gh ? pa : nullptr;
+        P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.ratio; P.eps = g.eps; P.relu = g.relu;
+        if (gh) {
+            auto kern = ratio_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, true>;
+            NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
+            kern<<<(unsigned)p.n_ratio, kRingNT, p.smem_ratio, st>>>(P);
+        } else {
+            auto kern = ratio_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, false>;
+            NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
+            kern<<<(unsigned)p.n_ratio, kRingNT, p.smem_ratio, st>>>(P);
+        }
+        launched();
+    }
+    {
+        KconvParams P;
+        int n = 0;
+        if (gz || gh) { P.in[n] = gden; P.out[n] = gt1; P.out_is_f32[n] = 1; ++n; }
+        if (gx) { P.in[n] = gnum; P.out[n] = gx; P.out_is_f32[n] = 0; ++n; }
+        for (int i = n; i < 2; ++i) { P.in[i] = nullptr; P.out[i] = nullptr; P.out_is_f32[i] = 0; }
+        P.h = h; P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.kconv;
+        if (n > 0) {
+            auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, kKconvMAXZ, VEC>;
+            NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
+            dim3 grid((unsigned)(BC * p.kconv.ndc * p.kconv.nth), n);
+            kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
+            launched();
+        }
+    }
+    if (gz || gh) {
+        GzParams P;
+        P.gt1 = gt1; P.z = z; P.gz = gz; P.h = h; P.bias = bias; P.partial = pb;
+        P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.gz; P.relu = g.relu;
+        if (gh) {
+            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, true>;
+            NDC_CUDA_TRY(set_smem(kern, p.smem_gz));
+            kern<<<(unsigned)p.n_gz, kRingNT, p.smem_gz, st>>>(P);
+        } else {
+            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, false>;
+            NDC_CUDA_TRY(set_smem(kern, p.smem_gz));
+            kern<<<(unsigned)p.n_gz, kRingNT, p.smem_gz, st>>>(P);
+        }
+        launched();
+    }
+    if (gh || gb) {
+        ReduceParams P;
+        P.partial_a = gh ? pa : nullptr;
+        P.partial_b = pb;
+        P.ctas_per_bc_a = (long long)p.ratio.ndc * p.ratio.nth;
+        P.ctas_per_bc_b = (long long)p.gz.ndc * p.gz.nth;
+        P.b_has_w = gh ? 1 : 0;
+        P.B = g.B; P.C = g.G; P.KT = g.KT; P.gh = gh; P.gb = gb;
+        reduce_kernel<<<g.G, 128, 0, st>>>(P);
+        launched();
+    }
+    return cudaGetLastError();
+}
+
+template <typename T, int KD, int KH, int KW>
+cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
+                           const float* h, const float* bias, const T* gout, T* gx, T* gz,
+                           float* gh, float* gb, void* ws, int dtype, cudaStream_t st) {
+    bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
+               aligned_for_vec(t1, dtype) && aligned_for_vec(gout, dtype);
+    if (gx) vec = vec && aligned_for_vec(gx, dtype);
+    if (gz) vec = vec && aligned_for_vec(gz, dtype);
+    return vec ? backward_launch<T, KD, KH, KW, true>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
+               : backward_launch<T, KD, KH, KW, false>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+}
+
+template <typename T>
+cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
+                     const float* h, const float* bias, const T* gout, T* gx, T* gz, float* gh,
+                     float* gb, void* ws, int dtype, cudaStream_t st) {
+    if (g.kD == 3)
+        return backward_shape<T, 3, 3, 3>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    if (g.kH == 5)
+        return backward_shape<T, 1, 5, 5>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    return backward_shape<T, 1, 3, 3>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+}
+
 // Whether the tiled kernels take this geometry (pointer alignment only affects vector width).
 inline bool covers(const Geo& g) {
     if (g.m != 1 || g.sc != SCH || !shape_supported(g.kD, g.kH, g.kW)) return false;
     Tiling t; size_t smem;
     const long long BC = (long long)g.B * g.G;
+    BwdPlan bp;
+    if (!plan_bwd_any(g, bp)) return false;
     if (g.kD == 3) return plan_fwd<3, 3, 3>(g.D, g.H, g.W, BC, t, smem);
     if (g.kH == 5) return plan_fwd<1, 5, 5>(g.D, g.H, g.W, BC, t, smem);
     return plan_fwd<1, 3, 3>(g.D, g.H, g.W, BC, t, smem);
