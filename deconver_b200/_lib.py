@@ -12,13 +12,13 @@ from ._build import LIB
 NDC_F32, NDC_BF16 = 0, 1
 NDC_OK = 0
 PATH_GENERIC, PATH_DEPTHWISE4 = 0, 1
+STATIC_WORKSPACE_BYTES = 16 * 1024 * 1024
 FLAG_FORCE_GENERIC = 1
 
 # every symbol `include/ndc_b200.h` declares
 SYMBOLS = (
     "ndc_version", "ndc_last_error", "ndc_status_string", "ndc_launch_count", "ndc_query",
-    "ndc_fwd",
-    "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_gconv",
+    "ndc_fwd", "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_bwd_static", "ndc_gconv",
 )
 
 
@@ -70,6 +70,8 @@ def load():
     lib.ndc_bwd_workspace_bytes.argtypes = [dp]
     lib.ndc_bwd.restype = ctypes.c_int
     lib.ndc_bwd.argtypes = [dp, vp, vp, vp, fp, fp, vp, vp, vp, fp, fp, vp, ctypes.c_size_t, vp]
+    lib.ndc_bwd_static.restype = ctypes.c_int
+    lib.ndc_bwd_static.argtypes = [dp, vp, vp, vp, fp, fp, vp, vp, vp, fp, fp, vp]
     lib.ndc_gconv.restype = ctypes.c_int
     lib.ndc_gconv.argtypes = [dp, vp, fp, fp, ctypes.c_int32, vp, vp]
     _lib = lib

@@ -2,6 +2,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "ndc_b200.h"
 #include "ndc_common.cuh"
@@ -197,6 +198,44 @@ int ndc_bwd(const NdcDesc* desc, const void* x, const void* z, const void* t1, c
             st);
     if (e != cudaSuccess) return cuda_fail(e, "ndc_bwd launch");
     return NDC_OK;
+}
+
+// Scratch of ndc_bwd_static.  In host code this name is only a stand-in for the symbol; the
+// device address is looked up per device below and that pointer is what the kernels get.
+static __device__ __align__(256) unsigned char g_static_workspace[NDC_STATIC_WORKSPACE_BYTES];
+
+int ndc_bwd_static(const NdcDesc* desc, const void* x, const void* z, const void* t1,
+                   const float* h, const float* bias, const void* gout, void* gx, void* gz,
+                   float* gh, float* gb, void* stream) {
+    NDC_TRY(validate(desc));
+    const size_t need = ndc_bwd_workspace_bytes(desc);
+    if (need > (size_t)NDC_STATIC_WORKSPACE_BYTES)
+        return fail(NDC_ERR_WORKSPACE,
+                    "ndc_bwd_static: this geometry needs %zu bytes of scratch, the built-in array "
+                    "holds %zu; use ndc_bwd with a caller-provided workspace",
+                    need, (size_t)NDC_STATIC_WORKSPACE_BYTES);
+    // one address per device, found on first use with that device current
+    constexpr int kMaxDevices = 64;
+    static void* addr[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(e, "ndc_bwd_static: cudaGetDevice");
+    if (dev < 0 || dev >= kMaxDevices)
+        return fail(NDC_ERR_UNSUPPORTED, "ndc_bwd_static: device ordinal %d is not supported", dev);
+    void* ws = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!addr[dev]) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_static_workspace);
+            if (e != cudaSuccess) return cuda_fail(e, "ndc_bwd_static: cudaGetSymbolAddress");
+            addr[dev] = p;
+        }
+        ws = addr[dev];
+    }
+    return ndc_bwd(desc, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws,
+                   (size_t)NDC_STATIC_WORKSPACE_BYTES, stream);
 }
 
 int ndc_gconv(const NdcDesc* desc, const void* in, const float* h, const float* bias,

@@ -134,6 +134,37 @@ int ndc_bwd(const NdcDesc *desc, const void *x, const void *z, const void *t1, c
             void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Size of the library-owned scratch array used by ndc_bwd_static.  Every GPU on which this
+ * library is loaded holds these bytes from load until the process exits.
+ */
+#define NDC_STATIC_WORKSPACE_BYTES (16u * 1024u * 1024u)
+
+/*
+ * ndc_bwd for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference project.  Some hosts of this library own no allocator they are allowed to call
+ * at the point where a backward pass runs: a plugin running inside another framework's
+ * memory plan, a real-time or embedded inference/training loop that forbids cudaMalloc
+ * after start-up, or code running while the process has handed all free device memory to a
+ * pool it does not control.  For them the scratch that ndc_bwd takes from the caller lives
+ * in a fixed array inside the library instead; inputs and outputs are still the caller's.
+ *
+ *  - Same arguments and results as ndc_bwd, minus the workspace.  No cudaMalloc, cudaFree or
+ *    any other allocating call is made.
+ *  - Limit: the geometry must need at most NDC_STATIC_WORKSPACE_BYTES of scratch
+ *    (ndc_bwd_workspace_bytes tells); larger ones are refused with NDC_ERR_WORKSPACE and a
+ *    message naming both numbers.  Roughly: batch * groups * 9 * D*H*W * 4 bytes must fit.
+ *  - The first call on each device looks up the array's device address (once per device,
+ *    with that device current).  Make that first call before starting any stream capture.
+ *  - All calls on a device share the one array and it keeps whatever the last call left in
+ *    it.  Nothing in it needs to start at zero: every value is written before it is read.
+ *    Two calls whose kernels can overlap on the GPU (different streams, or different host
+ *    threads) race on it; issue them on one stream or order them yourself.
+ */
+int ndc_bwd_static(const NdcDesc *desc, const void *x, const void *z, const void *t1,
+                   const float *h, const float *bias, const void *gout, void *gx, void *gz,
+                   float *gh, float *gb, void *stream);
+
+/*
  * Grouped convolution K (adjoint = 0: groups*sc -> groups*m channels) or its adjoint A
  * (adjoint = 1: groups*m -> groups*sc channels) of a tensor of dtype desc->dtype.
  * With adjoint = 0, `bias` (or NULL) and desc->relu_input are applied to the input as it is
