@@ -164,6 +164,13 @@ __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
             const long long off = (long long)d * HW + (long long)hrow * W;
+            // global strips first: their latency hides behind the tap sweep
+            float zv[SCH][VA], gv[SCH][VA];
+#pragma unroll
+            for (int j = 0; j < SCH; ++j) {
+                load_strip_global<T, VEC, VA>(zg + j * SP + off, w0, W, zv[j]);
+                load_strip_global<T, VEC, VA>(gg + j * SP + off, w0, W, gv[j]);
+            }
             float an[SCH][VA], ad[SCH][VA];
 #pragma unroll
             for (int j = 0; j < SCH; ++j)
@@ -198,15 +205,13 @@ __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
             // epilogue: gnum, gden, direct term (an/ad are overwritten with gnum/gden)
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                float zv[VA], gv[VA], dv[VA];
-                load_strip_global<T, VEC, VA>(zg + j * SP + off, w0, W, zv);
-                load_strip_global<T, VEC, VA>(gg + j * SP + off, w0, W, gv);
+                float dv[VA];
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
-                    float s = zv[v] + bj[j];
+                    float s = zv[j][v] + bj[j];
                     if (P.relu) s = fmaxf(s, 0.0f);
                     const float r = fast_div(1.0f, ad[j][v]);
-                    const float gr = gv[v] * r;
+                    const float gr = gv[j][v] * r;
                     const float gn = gr * s;
                     dv[v] = gr * an[j][v];
                     ad[j][v] = -(gn * an[j][v]) * r;
@@ -547,11 +552,18 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
                     if (w0 + v >= W) sv[j][v] = 0.0f;
                 }
             }
+            // the accumulators start from the direct term, loaded up front so that the global
+            // loads are in flight during the tap sweep
             float ag[SCH][VA];
 #pragma unroll
-            for (int j = 0; j < SCH; ++j)
+            for (int j = 0; j < SCH; ++j) {
+                if (gzg) {
+                    load_strip_global<T, VEC, VA>(gzg + j * SP + off, w0, W, ag[j]);
+                } else {
 #pragma unroll
-                for (int v = 0; v < VA; ++v) ag[j][v] = 0.0f;
+                    for (int v = 0; v < VA; ++v) ag[j][v] = 0.0f;
+                }
+            }
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd) {
                 const int q = d + PD - kd;
@@ -584,10 +596,9 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
 #pragma unroll
                 for (int j = 0; j < SCH; ++j) {
                     float dv[VA];
-                    load_strip_global<T, VEC, VA>(gzg + j * SP + off, w0, W, dv);
 #pragma unroll
                     for (int v = 0; v < VA; ++v) {
-                        float r = dv[v] + ag[j][v];
+                        float r = ag[j][v];
                         if (P.relu && !(pre[j][v] > 0.0f)) r = 0.0f;
                         if (w0 + v >= W) r = 0.0f;
                         dv[v] = r;
