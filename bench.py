@@ -38,9 +38,10 @@ WORKLOAD_NAME = ("single 3D NDC mixer layer fwd+bwd (dX, dK), fp32, X (2,64,64,6
                  "source 256 ch, K (256,1,3,3,3)")
 # measured on this pool's B200 with an FFMA-only kernel (profiles/fp32_fma_peak.md)
 FP32_FMA_PEAK_TFLOPS = 72.6
-# DRAM bytes per ndc_bwd call from an ncu capture, or None until one has been taken
-# (profiles/ names the capture); scaled to the bench workload by voxel count
-BWD_DRAM_TRAFFIC_BYTES = None
+# DRAM bytes (read + write) per ndc_bwd call: ncu capture at batch 1
+# (profiles/ndc_kernels_cfg3_b1_ncu_full.md: ratio 1444 MB + kconv 706 MB + gz 843 MB),
+# scaled by 2 to the bench workload's batch of 2 (traffic is proportional to voxels)
+BWD_DRAM_TRAFFIC_BYTES = 2 * (1444 + 706 + 843) * 1000 * 1000
 
 
 def load_peaks():
