@@ -2,10 +2,11 @@
 //
 //   ratio_kernel    per voxel: n = A(x)+eps, d = A(t1)+eps recomputed from shared-memory rings,
 //                   gnum = g*s/d, gden = -(gnum*n)/d (float32 scratch), the direct term
-//                   (g*n)/d (into the gz buffer), and two of the three filter-gradient
-//                   correlations:  sum_p gden[j,p] t1[p+pad-tau] + gnum[j,p] x[p+pad-tau]
+//                   (g*n)/d (into the gz buffer)
 //   kconv_kernel    K applied to a 4-channel float32 tensor with running sums along depth:
-//                   gt1 = K(gden) (scratch) and gx = K(gnum)
+//                   gt1 = K(gden) (scratch) and gx = K(gnum); the windows it loads for that
+//                   also feed two of the three filter-gradient correlations,
+//                   sum_q t1[q] gden[j, q+tau-pad]  and  sum_q x[q] gnum[j, q+tau-pad]
 //   gz_kernel       gz = [z+b>0] * (direct + A(gt1)) in place, gb = sum gz, and the third
 //                   correlation  sum_p s[j,p] gt1[p+pad-tau]
 //   reduce_kernel   fixed-order sum of the per-CTA partial filter/bias gradients
@@ -37,7 +38,8 @@ struct RingSmem {
         o = (o + 3) / 4 * 4;
         ring0 = o; o += ntensors * RING * plane_t;
         desc = o; o += KD > 1 ? 2 * (RT * t.NQ) : 0;
-        // the end-of-kernel reduction reuses the ring area: nthreads rows of (taps*4 + 5) floats
+        // the end-of-kernel reduction (nthreads > 0) reuses the ring area: nthreads rows of
+        // (taps*4 + 5) floats
         const int red = nthreads * (KD * KH * KW * SCH + 5);
         if (o - ring0 < red) o = ring0 + red;
         total_floats = o;
@@ -49,7 +51,6 @@ struct RatioParams {
     const float* h; const float* bias;
     float* gnum; float* gden;   // float32 scratch, source-sized
     void* gz;                   // direct term goes here (storage dtype), or NULL
-    float* partial;             // [cta][kPartialStride], or NULL
     int C, D, H, W;
     Tiling t;
     float eps;
@@ -72,14 +73,14 @@ __device__ __forceinline__ void cta_combine(float* scratch, const float (&acc)[N
     }
 }
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD>
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC>
 __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
     using L = RingSmem<KD, KH, KW>;
     constexpr int RING = L::RING;
     constexpr int NQA = 1 + (2 * PW + 3) / 4;
     extern __shared__ __align__(16) float smem[];
-    const L lay(P.t, 2, NT);
+    const L lay(P.t, 2, 0);
     const int tid = threadIdx.x;
     const int NQ = P.t.NQ, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
     const long long HW = (long long)H * W, SP = HW * D;
@@ -117,9 +118,6 @@ __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
-    float accw[WGRAD ? KT * SCH : 1];
-#pragma unroll
-    for (int k = 0; k < (WGRAD ? KT * SCH : 1); ++k) accw[k] = 0.0f;
     __syncthreads();
 
     const int qbase = d0 - PD - 1;
@@ -222,33 +220,6 @@ __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
                 store_strip_global<float, VEC, VA>(gdg + j * SP + off, w0, W, ad[j]);
                 if (dirg) store_strip_global<T, VEC, VA>(dirg + j * SP + off, w0, W, dv);
             }
-            if (WGRAD) {
-#pragma unroll
-                for (int kd = 0; kd < KD; ++kd) {
-                    const int q = d + PD - kd;
-                    if (q < 0 || q >= D) continue;
-                    const int slot = slot_of(q);
-#pragma unroll
-                    for (int kh = 0; kh < KH; ++kh) {
-                        const int rr = a_row + PH + PH - kh;
-                        float xv[4 * NQA], tv[4 * NQA];
-                        load_window<NQA, false>(xring + slot * lay.plane_t + rr * pitch, a_q + 1, xv);
-                        load_window<NQA, false>(tring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
-#pragma unroll
-                        for (int kw = 0; kw < KW; ++kw)
-#pragma unroll
-                            for (int j = 0; j < SCH; ++j) {
-                                float a = accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0];
-#pragma unroll
-                                for (int v = 0; v < VA; ++v) {
-                                    a = fmaf(ad[j][v], tv[v + 2 * PW - kw], a);
-                                    a = fmaf(an[j][v], xv[v + 2 * PW - kw], a);
-                                }
-                                accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] = a;
-                            }
-                    }
-                }
-            }
         }
         if (have) {
 #pragma unroll
@@ -265,8 +236,6 @@ __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
         }
         __syncthreads();
     }
-    if (WGRAD && P.partial)
-        cta_combine<WGRAD ? KT * SCH : 1, NT>(xring, accw, P.partial + (long long)blockIdx.x * kPartialStride);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -275,6 +244,8 @@ struct KconvParams {
     const float* in[2];     // gridDim.y selects: [0] gden -> gt1 (float32), [1] gnum -> gx (T)
     void* out[2];
     int out_is_f32[2];
+    const void* aux[2];     // single-channel tensor correlated with in[]: t1 for gden, x for gnum
+    float* partial[2];      // [cta][kPartialStride] records of the correlations, or NULL
     const float* h;
     int C, D, H, W;
     Tiling t;
@@ -296,13 +267,18 @@ struct KconvSmem {
         desc = o; o += KD > 1 ? 2 * (SCH * RS * t.NQ) : 0;
         total_floats = o;
     }
+    // with the correlations: room for the end-of-kernel combine (nthreads rows of taps*4+1)
+    __host__ __device__ KconvSmem(const Tiling& t, int nthreads) : KconvSmem(t) {
+        const int red = nthreads * (KD * KH * KW * SCH + 1);
+        if (total_floats - sbuf < red) total_floats = sbuf + red;
+    }
 };
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXZ, bool VEC>
-__global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
+template <typename T, int KD, int KH, int KW, int NT, int MAXZ, bool VEC, bool WGRAD>
+__global__ void __launch_bounds__(NT, WGRAD ? 2 : 3) kconv_kernel(const KconvParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = KconvSmem<KD, KH, KW>;
-    constexpr int WKP = L::WKP, NSB = L::NSB;
+    constexpr int WKP = L::WKP, NSB = L::NSB, KT = KD * KH * KW;
     constexpr int NQK = 2 + (2 * PW + 3) / 4;
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
@@ -347,6 +323,26 @@ __global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
     for (int a = 0; a < KD; ++a)
 #pragma unroll
         for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
+    // correlations: accw[tau][j] += aux[q] * in[j, q + tau - pad]; aux strips of the KD output
+    // planes the running sums stand for roll along with them
+    const T* auxg = WGRAD ? reinterpret_cast<const T*>(P.aux[which]) + (long long)bc * SP : nullptr;
+    float accw[WGRAD ? KT * SCH : 1];
+    float auxs[WGRAD ? KD : 1][VK];
+#pragma unroll
+    for (int k = 0; k < (WGRAD ? KT * SCH : 1); ++k) accw[k] = 0.0f;
+#pragma unroll
+    for (int a = 0; a < (WGRAD ? KD : 1); ++a)
+#pragma unroll
+        for (int v = 0; v < VK; ++v) auxs[a][v] = 0.0f;
+    auto aux_strip = [&](int q, float (&dst)[VK]) {   // strip of plane q, zero outside the chunk
+        if (k_ok && q >= d0 && q < d1)
+            load_strip_global<T, VEC, VK>(auxg + (long long)q * HW + (long long)(h0 + k_row) * W,
+                                          VK * k_strip, W, dst);
+        else {
+#pragma unroll
+            for (int v = 0; v < VK; ++v) dst[v] = 0.0f;
+        }
+    };
     __syncthreads();
 
     auto load_now = [&](int plane) {
@@ -362,10 +358,16 @@ __global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
     };
     const int p_first = d0 - PD, p_last = d1 - 1 + PD;
     if (p_first >= 0 && p_first < D) load_now(p_first);
+    if (WGRAD) {
+#pragma unroll
+        for (int kd = 0; kd < KD; ++kd) aux_strip(p_first + PD - kd, auxs[kd]);
+    }
     __syncthreads();
 
     for (int p = p_first; p <= p_last; ++p) {
         float4 zr[MAXZ];
+        float aux_next[VK];
+        if (WGRAD) aux_strip(p + 1 + PD, aux_next);   // plane that slot 0 stands for next step
         const bool have = KD > 1 && p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
         if (have) {
 #pragma unroll
@@ -383,26 +385,56 @@ __global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
         const bool q_need = qdone >= d0 && qdone < d1;
         auto accumulate = [&](int row, int strip, float (&acc)[KD][VK]) {
             const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + row * pitch;
-#pragma unroll 1
-            for (int kh = 0; kh < KH; ++kh) {
-#pragma unroll 1
-                for (int j = 0; j < SCH; ++j) {
-                    float sv[4 * NQK];
-                    load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
-                    float w[WKP];
+            auto body = [&](int kh, int j) {
+                float sv[4 * NQK];
+                load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
+                float w[WKP];
 #pragma unroll
-                    for (int q4 = 0; q4 < WKP / 4; ++q4) {
-                        const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + j) * WKP + 4 * q4);
-                        w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
-                    }
-#pragma unroll
-                    for (int kd = 0; kd < KD; ++kd)
-#pragma unroll
-                        for (int kw = 0; kw < KW; ++kw)
-#pragma unroll
-                            for (int v = 0; v < VK; ++v)
-                                acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
+                for (int q4 = 0; q4 < WKP / 4; ++q4) {
+                    const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + j) * WKP + 4 * q4);
+                    w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
                 }
+#pragma unroll
+                for (int kd = 0; kd < KD; ++kd)
+#pragma unroll
+                    for (int kw = 0; kw < KW; ++kw)
+#pragma unroll
+                        for (int v = 0; v < VK; ++v)
+                            acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
+                return 0;
+            };
+            if (WGRAD) {
+                // unrolled: every (kh, j) owns its own correlation accumulators
+#pragma unroll
+                for (int kh = 0; kh < KH; ++kh)
+#pragma unroll
+                    for (int j = 0; j < SCH; ++j) {
+                        float sv[4 * NQK];
+                        load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
+                        float w[WKP];
+#pragma unroll
+                        for (int q4 = 0; q4 < WKP / 4; ++q4) {
+                            const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + j) * WKP + 4 * q4);
+                            w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
+                        }
+#pragma unroll
+                        for (int kd = 0; kd < KD; ++kd)
+#pragma unroll
+                            for (int kw = 0; kw < KW; ++kw) {
+                                float a = accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0];
+#pragma unroll
+                                for (int v = 0; v < VK; ++v) {
+                                    acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
+                                    a = fmaf(auxs[WGRAD ? kd : 0][v], sv[v + kw], a);
+                                }
+                                accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] = a;
+                            }
+                    }
+            } else {
+#pragma unroll 1
+                for (int kh = 0; kh < KH; ++kh)
+#pragma unroll 1
+                    for (int j = 0; j < SCH; ++j) body(kh, j);
             }
         };
         auto finish = [&](int row, int strip, const float (&done)[VK]) {
@@ -418,15 +450,24 @@ __global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
 #pragma unroll
             for (int kd = KD - 1; kd > 0; --kd)
 #pragma unroll
-                for (int v = 0; v < VK; ++v) kacc[kd][v] = kacc[kd - 1][v];
+                for (int v = 0; v < VK; ++v) {
+                    kacc[kd][v] = kacc[kd - 1][v];
+                    if (WGRAD) auxs[WGRAD ? kd : 0][v] = auxs[WGRAD ? kd - 1 : 0][v];
+                }
 #pragma unroll
-            for (int v = 0; v < VK; ++v) kacc[0][v] = 0.0f;
+            for (int v = 0; v < VK; ++v) {
+                kacc[0][v] = 0.0f;
+                if (WGRAD) auxs[0][v] = aux_next[v];
+            }
         } else if (s_ok && q_need) {
 #pragma unroll 1
             for (int item = tid; item < TH * NS8; item += NT) {
                 float acc[KD][VK];
 #pragma unroll
                 for (int v = 0; v < VK; ++v) acc[0][v] = 0.0f;
+                if (WGRAD)
+                    load_strip_global<T, VEC, VK>(auxg + (long long)p * HW + (long long)(h0 + item / NS8) * W,
+                                                  VK * (item % NS8), W, auxs[0]);
                 accumulate(item / NS8, item % NS8, acc);
                 finish(item / NS8, item % NS8, acc[KD - 1]);
             }
@@ -444,6 +485,9 @@ __global__ void __launch_bounds__(NT, 3) kconv_kernel(const KconvParams P) {
         }
         __syncthreads();
     }
+    if (WGRAD && P.partial[which])
+        cta_combine<WGRAD ? KT * SCH : 1, NT>(sbuf, accw,
+                                              P.partial[which] + (long long)blockIdx.x * kPartialStride);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -639,7 +683,8 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
 // ------------------------------------------------------------------------------------------
 // gh[c][j][tau] = sum over CTAs of group c, in launch order, of both partial sets; gb likewise.
 struct ReduceParams {
-    const float* partial_a;   // ratio kernel records (or NULL)
+    const float* partial_a;   // kconv records, gden half (or NULL)
+    const float* partial_a2;  // kconv records, gnum half (or NULL)
     const float* partial_b;   // gz kernel records (or NULL)
     long long ctas_per_bc_a, ctas_per_bc_b;  // records per (sample, group) pair
     int b_has_w;              // the gz records carry filter sums
@@ -659,6 +704,9 @@ __global__ void __launch_bounds__(128) reduce_kernel(const ReduceParams P) {
         if (P.partial_a && is_w)
             for (long long i = 0; i < P.ctas_per_bc_a; ++i)
                 s += P.partial_a[(bc * P.ctas_per_bc_a + i) * kPartialStride + k];
+        if (P.partial_a2 && is_w)
+            for (long long i = 0; i < P.ctas_per_bc_a; ++i)
+                s += P.partial_a2[(bc * P.ctas_per_bc_a + i) * kPartialStride + k];
         if (P.partial_b && (is_b || P.b_has_w))
             for (long long i = 0; i < P.ctas_per_bc_b; ++i)
                 s += P.partial_b[(bc * P.ctas_per_bc_b + i) * kPartialStride + k];

@@ -103,23 +103,26 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
 
 // ---------------------------------------------------------------------------- backward
 
-constexpr int kRingNT = 128;    // ratio_kernel / gz_kernel threads
-constexpr int kRingMAXX = 4;    // prefetch registers (quads) per tensor
+constexpr int kRatioNT = 256;   // ratio_kernel threads
+constexpr int kRatioMAXX = 2;   // its prefetch registers (quads) per tensor
+constexpr int kRingNT = 128;    // gz_kernel threads
+constexpr int kRingMAXX = 4;
 constexpr int kKconvNT = 128;
 constexpr int kKconvMAXZ = 10;
 
 // Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
 template <int KD, int KH, int KW>
-inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, Tiling& t, size_t& smem_bytes) {
+inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, int maxx,
+                      int red_threads, Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
     t.NQ = (W + 3) / 4;
     t.pitch = row_pitch(W);
     int TH = H;
-    if (KD > 1) TH = std::min(TH, kRingNT * kRingMAXX / t.NQ - 2 * PH);
+    if (KD > 1) TH = std::min(TH, nt * maxx / t.NQ - 2 * PH);
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
-        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, kRingNT).total_floats * sizeof(float);
+        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, red_threads).total_floats * sizeof(float);
     };
     while (TH > 1 && (bytes(TH) > kSmemTwoPerSM || (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
@@ -144,7 +147,7 @@ inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& sme
     }
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
-        return (size_t)KconvSmem<KD, KH, KW>(q).total_floats * sizeof(float);
+        return (size_t)KconvSmem<KD, KH, KW>(q, kKconvNT).total_floats * sizeof(float);
     };
     while (TH > 1 && (bytes(TH) > 72 * 1024 || SCH * (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
@@ -158,27 +161,33 @@ inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& sme
 struct BwdPlan {
     Tiling ratio, kconv, gz;
     size_t smem_ratio, smem_kconv, smem_gz;
-    size_t off_gnum, off_gden, off_gt1, off_pa, off_pb, bytes;
-    long long n_ratio, n_gz;   // CTAs (= partial records)
+    size_t off_gnum, off_gden, off_gt1, off_gxtmp, off_pa, off_pa2, off_pb, bytes;
+    long long n_ratio, n_kconv, n_gz;   // CTAs (kconv: per tensor; = partial records)
 };
 
 template <int KD, int KH, int KW>
 inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     const long long BC = (long long)g.B * g.G;
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, p.ratio, p.smem_ratio)) return false;
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, kRatioNT, kRatioMAXX, 0, p.ratio, p.smem_ratio))
+        return false;
     if (!plan_kconv<KD, KH, KW>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, p.gz, p.smem_gz)) return false;
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, kRingNT, kRingMAXX, kRingNT, p.gz, p.smem_gz))
+        return false;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t src = (size_t)BC * SCH * g.SP * sizeof(float);
     const size_t flt = (size_t)BC * g.SP * sizeof(float);
     p.n_ratio = BC * p.ratio.ndc * p.ratio.nth;
+    p.n_kconv = BC * p.kconv.ndc * p.kconv.nth;
     p.n_gz = BC * p.gz.ndc * p.gz.nth;
+    const size_t rec = (size_t)kPartialStride * sizeof(float);
     p.off_gnum = 0;
     p.off_gden = up(src);
     p.off_gt1 = p.off_gden + up(src);
-    p.off_pa = p.off_gt1 + up(flt);
-    p.off_pb = p.off_pa + up((size_t)p.n_ratio * kPartialStride * sizeof(float));
-    p.bytes = p.off_pb + up((size_t)p.n_gz * kPartialStride * sizeof(float));
+    p.off_gxtmp = p.off_gt1 + up(flt);      // K(gnum) when the caller does not want gx
+    p.off_pa = p.off_gxtmp + up(flt);
+    p.off_pa2 = p.off_pa + up((size_t)p.n_kconv * rec);
+    p.off_pb = p.off_pa2 + up((size_t)p.n_kconv * rec);
+    p.bytes = p.off_pb + up((size_t)p.n_gz * rec);
     return true;
 }
 
@@ -210,35 +219,47 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
     float* gden = (float*)((char*)ws + p.off_gden);
     float* gt1 = (float*)((char*)ws + p.off_gt1);
     float* pa = (float*)((char*)ws + p.off_pa);
+    float* pa2 = (float*)((char*)ws + p.off_pa2);
     float* pb = (float*)((char*)ws + p.off_pb);
     {
         RatioParams P;
         P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;
-        P.gnum = gnum; P.gden = gden; P.gz = gz; P.partial = gh ? pa : nullptr;
+        P.gnum = gnum; P.gden = gden; P.gz = gz;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.ratio; P.eps = g.eps; P.relu = g.relu;
-        if (gh) {
-            auto kern = ratio_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, true>;
-            NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
-            kern<<<(unsigned)p.n_ratio, kRingNT, p.smem_ratio, st>>>(P);
-        } else {
-            auto kern = ratio_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, false>;
-            NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
-            kern<<<(unsigned)p.n_ratio, kRingNT, p.smem_ratio, st>>>(P);
-        }
+        auto kern = ratio_kernel<T, KD, KH, KW, kRatioNT, kRatioMAXX, VEC>;
+        NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
+        kern<<<(unsigned)p.n_ratio, kRatioNT, p.smem_ratio, st>>>(P);
         launched();
     }
     {
         KconvParams P;
         int n = 0;
-        if (gz || gh) { P.in[n] = gden; P.out[n] = gt1; P.out_is_f32[n] = 1; ++n; }
-        if (gx) { P.in[n] = gnum; P.out[n] = gx; P.out_is_f32[n] = 0; ++n; }
-        for (int i = n; i < 2; ++i) { P.in[i] = nullptr; P.out[i] = nullptr; P.out_is_f32[i] = 0; }
+        if (gz || gh) {
+            P.in[n] = gden; P.out[n] = gt1; P.out_is_f32[n] = 1; P.aux[n] = t1; P.partial[n] = gh ? pa : nullptr;
+            ++n;
+        }
+        if (gx || gh) {
+            // without gx the convolution result goes to scratch; the pass is still needed for
+            // its correlation
+            P.in[n] = gnum; P.out[n] = gx ? (void*)gx : (void*)((char*)ws + p.off_gxtmp);
+            P.out_is_f32[n] = 0; P.aux[n] = x; P.partial[n] = gh ? pa2 : nullptr;
+            ++n;
+        }
+        for (int i = n; i < 2; ++i) {
+            P.in[i] = nullptr; P.out[i] = nullptr; P.out_is_f32[i] = 0; P.aux[i] = nullptr; P.partial[i] = nullptr;
+        }
         P.h = h; P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.kconv;
         if (n > 0) {
-            auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, kKconvMAXZ, VEC>;
-            NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
-            dim3 grid((unsigned)(BC * p.kconv.ndc * p.kconv.nth), n);
-            kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
+            dim3 grid((unsigned)p.n_kconv, n);
+            if (gh) {
+                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, kKconvMAXZ, VEC, true>;
+                NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
+                kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
+            } else {
+                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, kKconvMAXZ, VEC, false>;
+                NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
+                kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
+            }
             launched();
         }
     }
@@ -260,8 +281,9 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
     if (gh || gb) {
         ReduceParams P;
         P.partial_a = gh ? pa : nullptr;
+        P.partial_a2 = gh ? pa2 : nullptr;
         P.partial_b = pb;
-        P.ctas_per_bc_a = (long long)p.ratio.ndc * p.ratio.nth;
+        P.ctas_per_bc_a = (long long)p.kconv.ndc * p.kconv.nth;
         P.ctas_per_bc_b = (long long)p.gz.ndc * p.gz.nth;
         P.b_has_w = gh ? 1 : 0;
         P.B = g.B; P.C = g.G; P.KT = g.KT; P.gh = gh; P.gb = gb;
