@@ -42,7 +42,7 @@ struct RingSmem {
         // (taps*4 + 5) floats
         const int red = nthreads * (KD * KH * KW * SCH + 5);
         if (o - ring0 < red) o = ring0 + red;
-        total_floats = o;
+        total_floats = (o + 3) / 4 * 4;
     }
 };
 
@@ -565,6 +565,22 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     __syncthreads();
 
     const int items = TH * NQ;
+    // z (and the direct term) of the next item are fetched while the current one is computed
+    constexpr int NSTR = 2 * SCH;
+    StripFetcher<T, VEC, NSTR, NT> fetch(smem + lay.total_floats);
+    auto strip_ptrs = [&](int d, int item, const T* (&ptr)[NSTR]) {
+        const long long off = (long long)d * HW + (long long)(h0 + item / NQ) * W + VA * (item % NQ);
+#pragma unroll
+        for (int j = 0; j < SCH; ++j) {
+            ptr[j] = zg + j * SP + off;
+            ptr[SCH + j] = (gzg ? gzg : zg) + j * SP + off;
+        }
+    };
+    if (tid < items && d0 < d1) {
+        const T* ptr[NSTR];
+        strip_ptrs(d0, tid, ptr);
+        fetch.request(ptr);
+    }
     for (int d = d0; d < d1; ++d) {
         float4 tr[MAXX];
         const int qn = d + PD + 1;
@@ -585,29 +601,34 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
             const long long off = (long long)d * HW + (long long)hrow * W;
+            float strips[NSTR][VA];
+            {
+                const T* ptr[NSTR];
+                strip_ptrs(d, item, ptr);
+                fetch.receive(ptr, w0, W, strips);
+                int nd = d, nitem = item + NT;
+                if (nitem >= items) { nitem = tid; nd = d + 1; }
+                if (nd < d1 && nitem < items) {
+                    strip_ptrs(nd, nitem, ptr);
+                    fetch.request(ptr);
+                }
+            }
             float sv[SCH][VA], pre[SCH][VA];
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                load_strip_global<T, VEC, VA>(zg + j * SP + off, w0, W, pre[j]);
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
-                    pre[j][v] += bj[j];
+                    pre[j][v] = strips[j][v] + bj[j];
                     sv[j][v] = P.relu ? fmaxf(pre[j][v], 0.0f) : pre[j][v];
                     if (w0 + v >= W) sv[j][v] = 0.0f;
                 }
             }
-            // the accumulators start from the direct term, loaded up front so that the global
-            // loads are in flight during the tap sweep
+            // the accumulators start from the direct term
             float ag[SCH][VA];
 #pragma unroll
-            for (int j = 0; j < SCH; ++j) {
-                if (gzg) {
-                    load_strip_global<T, VEC, VA>(gzg + j * SP + off, w0, W, ag[j]);
-                } else {
+            for (int j = 0; j < SCH; ++j)
 #pragma unroll
-                    for (int v = 0; v < VA; ++v) ag[j][v] = 0.0f;
-                }
-            }
+                for (int v = 0; v < VA; ++v) ag[j][v] = gzg ? strips[SCH + j][v] : 0.0f;
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd) {
                 const int q = d + PD - kd;

@@ -200,6 +200,64 @@ __device__ __forceinline__ void stage_chunk(float* plane, int soff, float4 v) {
     row[col_off<SWZ>(c + 3)] = v.w;
 }
 
+// ---- per-thread strip staging with cp.async ---------------------------------------------
+// A thread that walks over items (4-voxel strips) needs, for each item, a few strips of
+// per-voxel operands straight from HBM (z, upstream gradient, ...).  Loading them when the
+// item starts exposes the full memory latency at low occupancy, so the strips of the NEXT
+// item are requested with cp.async while the current item is computed.  Each thread owns two
+// slots (double buffer) of NSTR strips; slot layout [buffer][strip][thread] in 16-byte (8-byte
+// for bfloat16) units, so the read-back is conflict free.  Without VEC (rows not 16-byte
+// aligned) the strips are loaded directly instead.
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;\n" ::: "memory"); }
+
+template <typename T, bool VEC, int NSTR, int NT>
+struct StripFetcher {
+    static constexpr int kUnit = sizeof(T) == 4 ? 16 : 8;                    // bytes per strip
+    static constexpr int kFloats = VEC ? 2 * NSTR * NT * kUnit / 4 : 0;      // shared floats needed
+    char* base;
+    int buf;
+    __device__ __forceinline__ StripFetcher(float* smem_area) : base(reinterpret_cast<char*>(smem_area)), buf(0) {}
+    __device__ __forceinline__ char* slot(int b, int s) const {
+        return base + ((size_t)(b * NSTR + s) * NT + threadIdx.x) * kUnit;
+    }
+    // request the strips at src[0..NSTR) for the item after the current one
+    __device__ __forceinline__ void request(const T* const (&src)[NSTR]) {
+        if (!VEC) return;
+        buf ^= 1;
+#pragma unroll
+        for (int s = 0; s < NSTR; ++s) {
+            const unsigned dst = (unsigned)__cvta_generic_to_shared(slot(buf, s));
+            if (kUnit == 16)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src[s]) : "memory");
+            else
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src[s]) : "memory");
+        }
+        cp_async_commit();
+    }
+    // strips of the current item: the ones requested last (VEC) or loaded now (otherwise)
+    __device__ __forceinline__ void receive(const T* const (&src)[NSTR], int w0, int W, float (&v)[NSTR][VA]) {
+        if (VEC) {
+            cp_async_wait_all();
+#pragma unroll
+            for (int s = 0; s < NSTR; ++s) {
+                if (kUnit == 16) {
+                    const float4 t = *reinterpret_cast<const float4*>(slot(buf, s));
+                    v[s][0] = t.x; v[s][1] = t.y; v[s][2] = t.z; v[s][3] = t.w;
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(slot(buf, s));
+                    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    v[s][0] = a.x; v[s][1] = a.y; v[s][2] = b.x; v[s][3] = b.y;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int s = 0; s < NSTR; ++s) load_strip_global<T, false, VA>(src[s] - w0, w0, W, v[s]);
+        }
+    }
+};
+
 // x / (y) with one reciprocal approximation: |relative error| <= 2 ulp, y > 0 and normal.
 __device__ __forceinline__ float fast_div(float x, float y) { return __fdividef(x, y); }
 

@@ -113,7 +113,7 @@ constexpr int kKconvMAXZ = 10;
 // Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
 template <int KD, int KH, int KW>
 inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, int maxx,
-                      int red_threads, Tiling& t, size_t& smem_bytes) {
+                      int red_threads, size_t extra_bytes, Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
     t.NQ = (W + 3) / 4;
@@ -122,7 +122,8 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
     if (KD > 1) TH = std::min(TH, nt * maxx / t.NQ - 2 * PH);
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
-        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, red_threads).total_floats * sizeof(float);
+        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, red_threads).total_floats * sizeof(float) +
+               extra_bytes;
     };
     while (TH > 1 && (bytes(TH) > kSmemTwoPerSM || (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
@@ -168,10 +169,12 @@ struct BwdPlan {
 template <int KD, int KH, int KW>
 inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     const long long BC = (long long)g.B * g.G;
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, kRatioNT, kRatioMAXX, 0, p.ratio, p.smem_ratio))
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, kRatioNT, kRatioMAXX, 0, 0, p.ratio, p.smem_ratio))
         return false;
     if (!plan_kconv<KD, KH, KW>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, kRingNT, kRingMAXX, kRingNT, p.gz, p.smem_gz))
+    // gz_kernel also stages two sets of 8 strips per thread (z and the direct term)
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, kRingNT, kRingMAXX, kRingNT,
+                               (size_t)2 * 2 * SCH * kRingNT * 16, p.gz, p.smem_gz))
         return false;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t src = (size_t)BC * SCH * g.SP * sizeof(float);
