@@ -16,6 +16,8 @@
 // gradients are bitwise reproducible.
 #pragma once
 
+#include <type_traits>
+
 #include "ndc_dw4_common.cuh"
 
 namespace ndc {
@@ -264,22 +266,33 @@ struct KconvSmem {
         wK = o; o += KH * SCH * WKP;
         o = (o + 3) / 4 * 4;
         sbuf = o; o += NSB * plane_s;
-        desc = o; o += KD > 1 ? 2 * (SCH * RS * t.NQ) : 0;
+        desc = o; o += 2 * (SCH * RS * t.NQ);
         total_floats = o;
     }
-    // with the correlations: room for the end-of-kernel combine (nthreads rows of taps*4+1)
+    // with the correlations: room for the end-of-kernel combine (nthreads/4 rows of taps*4+1)
     __host__ __device__ KconvSmem(const Tiling& t, int nthreads) : KconvSmem(t) {
-        const int red = nthreads * (KD * KH * KW * SCH + 1);
+        const int red = (nthreads / SCH) * (KD * KH * KW * SCH + 1);
         if (total_floats - sbuf < red) total_floats = sbuf + red;
     }
 };
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXZ, bool VEC, bool WGRAD>
-__global__ void __launch_bounds__(NT, WGRAD ? 2 : 3) kconv_kernel(const KconvParams P) {
+// Thread layout: a warp covers 8 strips x 4 input channels (lane = channel*8 + strip lane), so a
+// thread convolves ONE channel: its running sums are partial and are added across the four
+// channel lanes when a plane completes, and its correlation accumulators are the taps of its
+// own channel only (27 instead of 108 registers).
+//
+// Source planes are float32 already, so they go from HBM to shared memory with cp.async
+// (no registers, no staging pass): rows are UNshifted here (shared column c holds w = c - 4),
+// 16-byte chunks land on 16-byte quads, and an 8-voxel strip reads a 4-quad window.
+// The KD running sums and their aux strips never move between registers: plane q lives in
+// slot q mod KD, and the step body exists in KD rotated copies.
+template <typename T, int KD, int KH, int KW, int NT, bool VEC, bool WGRAD>
+__global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = KconvSmem<KD, KH, KW>;
     constexpr int WKP = L::WKP, NSB = L::NSB, KT = KD * KH * KW;
-    constexpr int NQK = 2 + (2 * PW + 3) / 4;
+    constexpr int NG = NT / SCH;                 // strip slots per CTA
+    constexpr int NW = WGRAD ? KT : 1;           // correlation accumulators per thread
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
     const int tid = threadIdx.x;
@@ -300,194 +313,232 @@ __global__ void __launch_bounds__(NT, WGRAD ? 2 : 3) kconv_kernel(const KconvPar
     const float* ing = P.in[which] + (long long)bc * SCH * SP;
     float* outf = P.out_is_f32[which] ? reinterpret_cast<float*>(P.out[which]) + (long long)bc * SP : nullptr;
     T* outt = P.out_is_f32[which] ? nullptr : reinterpret_cast<T*>(P.out[which]) + (long long)bc * SP;
+    const T* auxg = WGRAD ? reinterpret_cast<const T*>(P.aux[which]) + (long long)bc * SP : nullptr;
 
     float* wK = smem + lay.wK;
     float* sbuf = smem + lay.sbuf;
     ChunkDesc* desc = reinterpret_cast<ChunkDesc*>(smem + lay.desc);
     for (int i = tid; i < NSB * lay.plane_s; i += NT) sbuf[i] = 0.0f;
     {
-        const float* hc = P.h + (long long)c * SCH * (KD * KH * KW);
-        for (int i = tid; i < KH * SCH * WKP; i += NT) {
+        const float* hc = P.h + (long long)c * SCH * KT;
+        for (int i = tid; i < KH * SCH * WKP; i += NT) {   // wK[kh][j][kd*KW + kw]
             const int e = i % WKP, j = (i / WKP) % SCH, kh = i / (WKP * SCH);
             float v = 0.0f;
-            if (e < KD * KW) v = hc[j * (KD * KH * KW) + ((e / KW) * KH + kh) * KW + e % KW];
+            if (e < KD * KW) v = hc[j * KT + ((e / KW) * KH + kh) * KW + e % KW];
             wK[i] = v;
         }
     }
+    // loader table: .goff = element offset in the plane (-1: row outside the volume),
+    // .soff = float offset of the destination quad in a plane buffer | (valid elements << 26)
     const int nz = SCH * RS * NQ;
-    if (KD > 1) build_descs(desc, SCH, RS, NQ, pitch, h0 - PH, H, W, SP, NT);
-    const int k_row = tid / NS8, k_strip = tid % NS8;   // row of the output band (no halo rows)
-    const bool k_ok = tid < TH * NS8;
-    float kacc[KD][VK];
+    for (int id = tid; id < nz; id += NT) {
+        const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
+        const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
+        ChunkDesc dsc;
+        dsc.goff = (h < 0 || h >= H) ? -1 : (int)(ch * SP) + h * W + w;
+        dsc.soff = ((ch * RS + r) * pitch + (phys_quad<true>(c4 + 1) << 2)) | (n << 26);
+        desc[id] = dsc;
+    }
+    const int lane = tid & 31;
+    const int jch = (lane >> 3) & 3;                       // this thread's input channel
+    const int slot = (tid >> 5) * 8 + (lane & 7);          // strip slot inside the CTA
+    const int n_items = TH * NS8;
+    float accw[NW];
 #pragma unroll
-    for (int a = 0; a < KD; ++a)
-#pragma unroll
-        for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
-    // correlations: accw[tau][j] += aux[q] * in[j, q + tau - pad]; aux strips of the KD output
-    // planes the running sums stand for roll along with them
-    const T* auxg = WGRAD ? reinterpret_cast<const T*>(P.aux[which]) + (long long)bc * SP : nullptr;
-    float accw[WGRAD ? KT * SCH : 1];
-    float auxs[WGRAD ? KD : 1][VK];
-#pragma unroll
-    for (int k = 0; k < (WGRAD ? KT * SCH : 1); ++k) accw[k] = 0.0f;
-#pragma unroll
-    for (int a = 0; a < (WGRAD ? KD : 1); ++a)
-#pragma unroll
-        for (int v = 0; v < VK; ++v) auxs[a][v] = 0.0f;
-    auto aux_strip = [&](int q, float (&dst)[VK]) {   // strip of plane q, zero outside the chunk
-        if (k_ok && q >= d0 && q < d1)
-            load_strip_global<T, VEC, VK>(auxg + (long long)q * HW + (long long)(h0 + k_row) * W,
-                                          VK * k_strip, W, dst);
-        else {
-#pragma unroll
-            for (int v = 0; v < VK; ++v) dst[v] = 0.0f;
-        }
-    };
+    for (int k = 0; k < NW; ++k) accw[k] = 0.0f;
     __syncthreads();
 
-    auto load_now = [&](int plane) {
+    // plane -> shared buffer: asynchronous 16-byte copies where rows allow, else through registers
+    auto copy_plane = [&](int plane) {
         const float* src = ing + (long long)plane * HW;
         float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
         for (int id = tid; id < nz; id += NT) {
-            const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
-            const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
-            if (h < 0 || h >= H) continue;
-            stage_chunk<PW, true>(dst, ((ch * RS + r) * pitch) | (w << 16) | (n << 26),
-                                  load4<float, VEC>(src + ch * SP + (long long)h * W + w, n));
+            const ChunkDesc dsc = desc[id];
+            if (dsc.goff < 0) continue;
+            float* q = dst + (dsc.soff & 0x3ffffff);
+            if (VEC) {
+                const unsigned sa = (unsigned)__cvta_generic_to_shared(q);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(src + dsc.goff) : "memory");
+            } else {
+                *reinterpret_cast<float4*>(q) = load4<float, false>(src + dsc.goff, (dsc.soff >> 26) & 7);
+            }
+        }
+        if (VEC) cp_async_commit();
+    };
+    // one source row of this thread's channel feeds KD output planes (and their correlations);
+    // output plane p+PD-kd lives in slot (R + PD - kd) mod KD, R = rotation of this step
+    auto accumulate = [&](auto rot, int p, int row, int strip, float (&acc)[KD][VK],
+                          const float (&aux)[WGRAD ? KD : 1][VK]) {
+        constexpr int R = decltype(rot)::value;
+        const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + (jch * RS + row) * pitch;
+        int qo[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) qo[q] = phys_quad<true>(2 * strip + q) << 2;
+#pragma unroll
+        for (int kh = 0; kh < KH; ++kh) {
+            float sv[16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const float4 t = *reinterpret_cast<const float4*>(sp + kh * pitch + qo[q]);
+                sv[4 * q] = t.x; sv[4 * q + 1] = t.y; sv[4 * q + 2] = t.z; sv[4 * q + 3] = t.w;
+            }
+            float w[WKP];
+#pragma unroll
+            for (int q4 = 0; q4 < WKP / 4; ++q4) {
+                const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + jch) * WKP + 4 * q4);
+                w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
+            }
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd) {
+                constexpr int dummy = 0; (void)dummy;
+                const int sl = (R + PD - kd + 2 * KD) % KD;
+#pragma unroll
+                for (int kw = 0; kw < KW; ++kw) {
+                    float a = WGRAD ? accw[WGRAD ? (kd * KH + kh) * KW + kw : 0] : 0.0f;
+#pragma unroll
+                    for (int v = 0; v < VK; ++v) {
+                        acc[sl][v] = fmaf(sv[4 - PW + v + kw], w[kd * KW + kw], acc[sl][v]);
+                        if (WGRAD) a = fmaf(aux[WGRAD ? sl : 0][v], sv[4 - PW + v + kw], a);
+                    }
+                    if (WGRAD) accw[WGRAD ? (kd * KH + kh) * KW + kw : 0] = a;
+                }
+            }
         }
     };
-    const int p_first = d0 - PD, p_last = d1 - 1 + PD;
-    if (p_first >= 0 && p_first < D) load_now(p_first);
-    if (WGRAD) {
+    // add the four channel lanes' partial sums; every lane ends up owning two voxels of the strip
+    auto finish = [&](int q, int row, int strip, const float (&part)[VK]) {
+        float h4[4];
+        const bool hi = jch & 2;
 #pragma unroll
-        for (int kd = 0; kd < KD; ++kd) aux_strip(p_first + PD - kd, auxs[kd]);
-    }
+        for (int i = 0; i < 4; ++i) {
+            const float send = hi ? part[i] : part[4 + i];
+            const float keep = hi ? part[4 + i] : part[i];
+            h4[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+        }
+        const bool odd = jch & 1;
+        float o2[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const float send = odd ? h4[i] : h4[2 + i];
+            const float keep = odd ? h4[2 + i] : h4[i];
+            o2[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+        }
+        if (row >= 0) {
+            const int w0 = VK * strip + (hi ? 4 : 0) + (odd ? 2 : 0);
+            const long long off = (long long)q * HW + (long long)(h0 + row) * W + w0;
+            if (VEC) {
+                if (w0 < W) {
+                    if (outf) *reinterpret_cast<float2*>(outf + off) = make_float2(o2[0], o2[1]);
+                    else if (sizeof(T) == 4) *reinterpret_cast<float2*>(outt + off) = make_float2(o2[0], o2[1]);
+                    else *reinterpret_cast<__nv_bfloat162*>(outt + off) = __floats2bfloat162_rn(o2[0], o2[1]);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 2; ++i)
+                    if (w0 + i < W) {
+                        if (outf) outf[off + i] = o2[i];
+                        else outt[off + i] = from_f32<T>(o2[i]);
+                    }
+            }
+        }
+    };
+
+    const int p_first = d0 - PD, p_last = d1 - 1 + PD;
+    if (p_first >= 0 && p_first < D) copy_plane(p_first);
+    if (VEC) cp_async_wait_all();
     __syncthreads();
 
-    for (int p = p_first; p <= p_last; ++p) {
-        float4 zr[MAXZ];
-        float aux_next[VK];
-        if (WGRAD) aux_strip(p + 1 + PD, aux_next);   // plane that slot 0 stands for next step
-        const bool have = KD > 1 && p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
-        if (have) {
+    if (KD > 1) {
+        // ---- marching: one strip per thread group, running sums along depth
+        const bool k_ok = slot < n_items;
+        const int k_row = k_ok ? slot / NS8 : 0, k_strip = k_ok ? slot % NS8 : 0;
+        float kacc[KD][VK], auxs[WGRAD ? KD : 1][VK];
 #pragma unroll
-            for (int i = 0; i < MAXZ; ++i) {
-                const int id = tid + i * NT;
-                if (id < nz) {
-                    const ChunkDesc dsc = desc[id];
-                    if (dsc.goff >= 0)
-                        zr[i] = load4<float, VEC>(ing + (long long)(p + 1) * HW + dsc.goff, desc_n(dsc.soff));
-                }
+        for (int a = 0; a < KD; ++a)
+#pragma unroll
+            for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
+        auto aux_strip = [&](int q, float (&dst)[VK]) {   // strip of plane q, zero outside the chunk
+            if (k_ok && q >= d0 && q < d1)
+                load_strip_global<T, VEC, VK>(auxg + (long long)q * HW + (long long)(h0 + k_row) * W,
+                                              VK * k_strip, W, dst);
+            else {
+#pragma unroll
+                for (int v = 0; v < VK; ++v) dst[v] = 0.0f;
             }
+        };
+        // plane q lives in slot (q - p_first) mod KD: at the first step (rotation 0) output plane
+        // p_first + PD - kd is slot (PD - kd) mod KD
+        if (WGRAD) {
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd) aux_strip(p_first + PD - kd, auxs[WGRAD ? (PD - kd + KD) % KD : 0]);
         }
-        const bool s_ok = p >= 0 && p < D;
-        const int qdone = p - PD;
-        const bool q_need = qdone >= d0 && qdone < d1;
-        auto accumulate = [&](int row, int strip, float (&acc)[KD][VK]) {
-            const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + row * pitch;
-            auto body = [&](int kh, int j) {
-                float sv[4 * NQK];
-                load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
-                float w[WKP];
-#pragma unroll
-                for (int q4 = 0; q4 < WKP / 4; ++q4) {
-                    const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + j) * WKP + 4 * q4);
-                    w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
-                }
-#pragma unroll
-                for (int kd = 0; kd < KD; ++kd)
-#pragma unroll
-                    for (int kw = 0; kw < KW; ++kw)
-#pragma unroll
-                        for (int v = 0; v < VK; ++v)
-                            acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
-                return 0;
-            };
-            if (WGRAD) {
-                // unrolled: every (kh, j) owns its own correlation accumulators
-#pragma unroll
-                for (int kh = 0; kh < KH; ++kh)
-#pragma unroll
-                    for (int j = 0; j < SCH; ++j) {
-                        float sv[4 * NQK];
-                        load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
-                        float w[WKP];
-#pragma unroll
-                        for (int q4 = 0; q4 < WKP / 4; ++q4) {
-                            const float4 t = *reinterpret_cast<const float4*>(wK + (kh * SCH + j) * WKP + 4 * q4);
-                            w[4 * q4] = t.x; w[4 * q4 + 1] = t.y; w[4 * q4 + 2] = t.z; w[4 * q4 + 3] = t.w;
-                        }
-#pragma unroll
-                        for (int kd = 0; kd < KD; ++kd)
-#pragma unroll
-                            for (int kw = 0; kw < KW; ++kw) {
-                                float a = accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0];
-#pragma unroll
-                                for (int v = 0; v < VK; ++v) {
-                                    acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
-                                    a = fmaf(auxs[WGRAD ? kd : 0][v], sv[v + kw], a);
-                                }
-                                accw[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] = a;
-                            }
-                    }
-            } else {
-#pragma unroll 1
-                for (int kh = 0; kh < KH; ++kh)
-#pragma unroll 1
-                    for (int j = 0; j < SCH; ++j) body(kh, j);
-            }
-        };
-        auto finish = [&](int row, int strip, const float (&done)[VK]) {
-            const long long off = (long long)qdone * HW + (long long)(h0 + row) * W;
-            if (outf) store_strip_global<float, VEC, VK>(outf + off, VK * strip, W, done);
-            else store_strip_global<T, VEC, VK>(outt + off, VK * strip, W, done);
-        };
-        if (KD > 1) {
-            if (k_ok) {
-                if (s_ok) accumulate(k_row, k_strip, kacc);
-                if (q_need) finish(k_row, k_strip, kacc[KD - 1]);
-            }
-#pragma unroll
-            for (int kd = KD - 1; kd > 0; --kd)
-#pragma unroll
-                for (int v = 0; v < VK; ++v) {
-                    kacc[kd][v] = kacc[kd - 1][v];
-                    if (WGRAD) auxs[WGRAD ? kd : 0][v] = auxs[WGRAD ? kd - 1 : 0][v];
-                }
+        auto step = [&](auto rot, int p) {
+            constexpr int R = decltype(rot)::value;
+            constexpr int DONE = (R - PD + 2 * KD) % KD;     // slot of plane p-PD, reused for p+1+PD
+            float aux_next[VK];
+            if (WGRAD) aux_strip(p + 1 + PD, aux_next);
+            const bool have = p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
+            if (have) copy_plane(p + 1);
+            const int qdone = p - PD;
+            if (k_ok && p >= 0 && p < D) accumulate(rot, p, k_row, k_strip, kacc, auxs);
+            if (qdone >= d0 && qdone < d1) finish(qdone, k_ok ? k_row : -1, k_strip, kacc[DONE]);
 #pragma unroll
             for (int v = 0; v < VK; ++v) {
-                kacc[0][v] = 0.0f;
-                if (WGRAD) auxs[0][v] = aux_next[v];
+                kacc[DONE][v] = 0.0f;
+                if (WGRAD) auxs[WGRAD ? DONE : 0][v] = aux_next[v];
             }
-        } else if (s_ok && q_need) {
-#pragma unroll 1
-            for (int item = tid; item < TH * NS8; item += NT) {
-                float acc[KD][VK];
-#pragma unroll
-                for (int v = 0; v < VK; ++v) acc[0][v] = 0.0f;
-                if (WGRAD)
-                    load_strip_global<T, VEC, VK>(auxg + (long long)p * HW + (long long)(h0 + item / NS8) * W,
-                                                  VK * (item % NS8), W, auxs[0]);
-                accumulate(item / NS8, item % NS8, acc);
-                finish(item / NS8, item % NS8, acc[KD - 1]);
-            }
-        }
-        if (have) {
-            float* dst = sbuf + ((p + 1) & (NSB - 1)) * lay.plane_s;
-#pragma unroll
-            for (int i = 0; i < MAXZ; ++i) {
-                const int id = tid + i * NT;
-                if (id < nz) {
-                    const ChunkDesc dsc = desc[id];
-                    if (dsc.goff >= 0) stage_chunk<PW, true>(dst, dsc.soff, zr[i]);
-                }
+            if (VEC) cp_async_wait_all();
+            __syncthreads();
+        };
+        int p = p_first;
+        while (p <= p_last) {
+            step(std::integral_constant<int, 0>{}, p++);
+            if (p > p_last) break;
+            if (KD > 1) step(std::integral_constant<int, 1 % KD>{}, p++);
+            if (p > p_last) break;
+            if (KD > 2) step(std::integral_constant<int, 2 % KD>{}, p++);
+            if (KD > 3) {   // wider depth kernels: remaining rotations
+                if (p > p_last) break;
+                step(std::integral_constant<int, 3 % KD>{}, p++);
+                if (p > p_last) break;
+                if (KD > 4) step(std::integral_constant<int, 4 % KD>{}, p++);
             }
         }
-        __syncthreads();
+    } else {
+        // ---- no depth taps: every plane is its own chunk, strips are looped over.  All lanes of
+        // a warp run the same number of rounds (the channel lanes exchange partial sums).
+        const int p = p_first;
+        if (p >= 0 && p < D) {
+            const int rounds = (n_items + NG - 1) / NG;
+            for (int r = 0; r < rounds; ++r) {
+                const int item = slot + r * NG;
+                const bool ok = item < n_items;
+                const int row = ok ? item / NS8 : 0, strip = ok ? item % NS8 : 0;
+                float acc[KD][VK], aux[WGRAD ? KD : 1][VK];
+#pragma unroll
+                for (int v = 0; v < VK; ++v) { acc[0][v] = 0.0f; aux[0][v] = 0.0f; }
+                if (WGRAD && ok)
+                    load_strip_global<T, VEC, VK>(auxg + (long long)p * HW + (long long)(h0 + row) * W,
+                                                  VK * strip, W, aux[0]);
+                if (ok) accumulate(std::integral_constant<int, 0>{}, p, row, strip, acc, aux);
+                finish(p, ok ? row : -1, strip, acc[0]);
+            }
+        }
     }
-    if (WGRAD && P.partial[which])
-        cta_combine<WGRAD ? KT * SCH : 1, NT>(sbuf, accw,
-                                              P.partial[which] + (long long)blockIdx.x * kPartialStride);
+    if (WGRAD && P.partial[which]) {
+        // per-CTA combine in a fixed order: slot-major scratch rows of taps*4 (+1 pad) floats
+        constexpr int LD = KT * SCH + 1;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < NW; ++k) sbuf[slot * LD + k * SCH + jch] = accw[k];
+        __syncthreads();
+        float* out = P.partial[which] + (long long)blockIdx.x * kPartialStride;
+        for (int k = tid; k < KT * SCH; k += NT) {
+            float s = 0.0f;
+            for (int i = 0; i < NG; ++i) s += sbuf[i * LD + k];
+            out[k] = s;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------

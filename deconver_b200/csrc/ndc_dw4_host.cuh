@@ -107,8 +107,7 @@ constexpr int kRatioNT = 256;   // ratio_kernel threads
 constexpr int kRatioMAXX = 2;   // its prefetch registers (quads) per tensor
 constexpr int kRingNT = 128;    // gz_kernel threads
 constexpr int kRingMAXX = 4;
-constexpr int kKconvNT = 128;
-constexpr int kKconvMAXZ = 10;
+constexpr int kKconvNT = 192;   // 48 strip slots x 4 channel lanes
 
 // Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
 template <int KD, int KH, int KW>
@@ -143,8 +142,7 @@ inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& sme
     const int NS8 = (t.NQ + 1) / 2;
     int TH = H;
     if (KD > 1) {
-        TH = std::min(TH, kKconvNT / NS8);
-        TH = std::min(TH, kKconvNT * kKconvMAXZ / (SCH * t.NQ) - 2 * PH);
+        TH = std::min(TH, (kKconvNT / SCH) / NS8);
     }
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
@@ -255,11 +253,11 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         if (n > 0) {
             dim3 grid((unsigned)p.n_kconv, n);
             if (gh) {
-                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, kKconvMAXZ, VEC, true>;
+                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, true>;
                 NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
                 kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
             } else {
-                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, kKconvMAXZ, VEC, false>;
+                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, false>;
                 NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
                 kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
             }
