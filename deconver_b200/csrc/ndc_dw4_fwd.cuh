@@ -6,9 +6,11 @@
 // chunk and keeps the planes it needs in shared-memory rings.  Per step p (a source plane):
 //
 //   prefetch   z plane p+1 and x plane p-PD into registers (global loads in flight)
-//   K phase    every K-thread owns an 8-voxel strip of the t1 band (TH + 2*PH rows) and keeps
-//              KD running sums, one per t1 plane that source plane p contributes to; plane
-//              p-PD is complete after this step and goes to the t1 ring (and to HBM)
+//   K phase    an 8-voxel strip of the t1 band (TH + 2*PH rows) is shared by two threads, each
+//              convolving two of the four source channels; each keeps KD partial running
+//              sums, one per t1 plane that source plane p contributes to; plane p-PD is
+//              complete after this step: the two halves are added (one shuffle) and go to
+//              the t1 ring (and to HBM)
 //   stage      the prefetched planes are rectified/biased and written to shared memory
 //   barrier
 //   A phase    output plane d = p-2*PD, 4-voxel strips: A(x) and A(t1) from the rings,
@@ -63,7 +65,6 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = FwdSmem<KD, KH, KW>;
     constexpr int WKP = L::WKP, RING = L::RING, NSB = L::NSB;
-    constexpr int NQK = 2 + (2 * PW + 3) / 4;   // quads in an 8-strip window (8 + 2*PW floats)
     constexpr int NQA = 1 + (2 * PW + 3) / 4;   // quads in a 4-strip window (4 + 2*PW floats)
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
@@ -114,17 +115,35 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         }
     }
     const int nz = SCH * RS * NQ, nx = RT * NQ;
+    // The source buffer is UNshifted (shared column c holds w = c - 4) and swizzled: 16-byte
+    // chunks of z land on whole quads, and an 8-voxel strip reads a 4-quad window.
+    auto z_soff = [&](int ch, int r, int c4, int n) {
+        return ((ch * RS + r) * pitch + (phys_quad<true>(c4 + 1) << 2)) | (n << 26) | (ch << 29);
+    };
     if (KD > 1) {
-        build_descs(zdesc, SCH, RS, NQ, pitch, h0 - 2 * PH, H, W, SP, NT);
+        for (int id = tid; id < nz; id += NT) {
+            const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
+            const int h = h0 - 2 * PH + r, w = 4 * c4;
+            ChunkDesc dsc;
+            dsc.goff = (h < 0 || h >= H) ? -1 : (int)(ch * SP) + h * W + w;
+            dsc.soff = z_soff(ch, r, c4, min(4, W - w));
+            zdesc[id] = dsc;
+        }
         build_descs(xdesc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
     }
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
 
-    // ---- this thread's K strip (8 voxels of one row of the t1 band) and its running sums
-    const int k_row = tid / NS8, k_strip = tid % NS8;
-    const bool k_ok = tid < (TH + 2 * PH) * NS8 && h0 - PH + k_row >= 0 && h0 - PH + k_row < H;
+    // ---- this thread's K strip (8 voxels of one row of the t1 band), its channel pair and
+    // its partial running sums.  lane = pair*16 + strip lane: a quarter-warp reads 8
+    // consecutive strips of one channel.
+    constexpr int NG = NT / 2;                              // strip slots per CTA
+    const int cpair = (tid >> 4) & 1;
+    const int k_slot = (tid >> 5) * 16 + (tid & 15);
+    const int n_kitems = (TH + 2 * PH) * NS8;
+    const int k_row = k_slot < n_kitems ? k_slot / NS8 : 0, k_strip = k_slot < n_kitems ? k_slot % NS8 : 0;
+    const bool k_ok = k_slot < n_kitems && h0 - PH + k_row >= 0 && h0 - PH + k_row < H;
     float kacc[KD][VK];
 #pragma unroll
     for (int a = 0; a < KD; ++a)
@@ -166,7 +185,8 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int id = tid + i * NT;
             if (id < nz) {
                 const ChunkDesc dsc = zdesc[id];
-                if (dsc.goff >= 0) stage_chunk<PW, true>(dst, dsc.soff, rectify(reg[i], dsc.soff));
+                if (dsc.goff >= 0)
+                    *reinterpret_cast<float4*>(dst + (dsc.soff & 0x3ffffff)) = rectify(reg[i], dsc.soff);
             }
         }
     };
@@ -201,9 +221,9 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
             const int h = h0 - 2 * PH + r, w = 4 * c4, n = min(4, W - w);
             if (h < 0 || h >= H) continue;
-            const int soff = ((ch * RS + r) * pitch) | (w << 16) | (n << 26) | (ch << 29);
+            const int soff = z_soff(ch, r, c4, n);
             const float4 v = load4<T, VEC>(src + ch * SP + (long long)h * W + w, n);
-            stage_chunk<PW, true>(dst, soff, rectify(v, soff));
+            *reinterpret_cast<float4*>(dst + (soff & 0x3ffffff)) = rectify(v, soff);
         }
     };
     auto load_x_now = [&](int plane, int slot) {
@@ -234,6 +254,17 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         const bool have_x = KD > 1 && xq >= 0 && xq < D && xq >= d0 - PD && xq <= d1 - 1 + PD;
         if (have_z) fetch_z(zr, p + 1);
         if (have_x) fetch_x(xr, xq);
+        // z of this thread's first A strip of this step: requested now, used after the K phase
+        float zpre[SCH][VA];
+        const int d_now = p - 2 * PD;
+        const bool a_now = false && d_now >= d0 && d_now < d1 && tid < a_items;
+        if (a_now) {
+#pragma unroll
+            for (int j = 0; j < SCH; ++j)
+                load_strip_global<T, VEC, VA>(zg + j * SP + (long long)d_now * HW +
+                                                  (long long)(h0 + tid / NQ) * W,
+                                              VA * (tid % NQ), W, zpre[j]);
+        }
 
         // -------- K phase: source plane p feeds t1 planes p+PD-kd
         const bool s_ok = p >= 0 && p < D;
@@ -241,13 +272,22 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         const bool q_need = qdone >= d0 - PD && qdone <= d1 - 1 + PD && qdone >= 0 && qdone < D;
         auto k_accumulate = [&](int row, int strip, float (&acc)[KD][VK]) {
             const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + row * pitch;
+            int qo[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) qo[q] = phys_quad<true>(2 * strip + q) << 2;
             // rolled on purpose: the body is the unit the instruction cache holds
 #pragma unroll 1
             for (int kh = 0; kh < KH; ++kh) {
-#pragma unroll 1
-                for (int j = 0; j < SCH; ++j) {
-                    float sv[4 * NQK];
-                    load_window<NQK, true>(sp + (j * RS + kh) * pitch, 2 * strip + 1, sv);
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int j = 2 * cpair + jj;
+                    const float* rp = sp + (j * RS + kh) * pitch;
+                    float sv[16];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float4 t = *reinterpret_cast<const float4*>(rp + qo[q]);
+                        sv[4 * q] = t.x; sv[4 * q + 1] = t.y; sv[4 * q + 2] = t.z; sv[4 * q + 3] = t.w;
+                    }
                     float w[WKP];
 #pragma unroll
                     for (int q4 = 0; q4 < WKP / 4; ++q4) {
@@ -261,25 +301,32 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
                         for (int kw = 0; kw < KW; ++kw)
 #pragma unroll
                             for (int v = 0; v < VK; ++v)
-                                acc[kd][v] = fmaf(sv[v + kw], w[kd * KW + kw], acc[kd][v]);
+                                acc[kd][v] = fmaf(sv[4 - PW + v + kw], w[kd * KW + kw], acc[kd][v]);
                 }
             }
         };
-        auto k_finish = [&](int row, int strip, const float (&done)[VK]) {
-            const int w0 = VK * strip;
-            float tv[VK];
+        // add the two channel halves; each lane then owns one quad of the strip.  `row < 0`
+        // marks a lane that only takes part in the exchange.
+        auto k_finish = [&](int row, int strip, const float (&part)[VK]) {
+            float tv[VA];
 #pragma unroll
-            for (int v = 0; v < VK; ++v) tv[v] = (w0 + v < W) ? done[v] : 0.0f;
-            store_strip<VK, PW, false>(t1ring + slot_of(qdone) * lay.plane_t + row * pitch, w0, tv);
+            for (int i = 0; i < VA; ++i) {
+                const float send = cpair ? part[i] : part[VA + i];
+                const float keep = cpair ? part[VA + i] : part[i];
+                tv[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+            if (row < 0) return;
+            const int w0 = VK * strip + VA * cpair;
+#pragma unroll
+            for (int v = 0; v < VA; ++v) if (w0 + v >= W) tv[v] = 0.0f;
+            store_strip<VA, PW, false>(t1ring + slot_of(qdone) * lay.plane_t + row * pitch, w0, tv);
             const int h = h0 - PH + row;
             if (qdone >= d0 && qdone < d1 && row >= PH && row < PH + TH)
-                store_strip_global<T, VEC, VK>(tg + (long long)qdone * HW + (long long)h * W, w0, W, tv);
+                store_strip_global<T, VEC, VA>(tg + (long long)qdone * HW + (long long)h * W, w0, W, tv);
         };
         if (KD > 1) {
-            if (k_ok) {
-                if (s_ok) k_accumulate(k_row, k_strip, kacc);
-                if (q_need) k_finish(k_row, k_strip, kacc[KD - 1]);
-            }
+            if (k_ok && s_ok) k_accumulate(k_row, k_strip, kacc);
+            if (q_need) k_finish(k_ok ? k_row : -1, k_strip, kacc[KD - 1]);
             // rotate the running sums: slot kd now stands for plane (p+1)+PD-kd
 #pragma unroll
             for (int kd = KD - 1; kd > 0; --kd)
@@ -289,16 +336,19 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             for (int v = 0; v < VK; ++v) kacc[0][v] = 0.0f;
         } else if (s_ok && q_need) {
             // no depth taps: nothing persists between planes, so strips are simply looped over
+            // (all lanes run every round: the channel halves exchange partial sums)
+            const int rounds = (n_kitems + NG - 1) / NG;
 #pragma unroll 1
-            for (int item = tid; item < (TH + 2 * PH) * NS8; item += NT) {
-                const int row = item / NS8, strip = item % NS8;
+            for (int r = 0; r < rounds; ++r) {
+                const int item = k_slot + r * NG;
+                const int row = item < n_kitems ? item / NS8 : 0, strip = item < n_kitems ? item % NS8 : 0;
                 const int h = h0 - PH + row;
-                if (h < 0 || h >= H) continue;
+                const bool ok = item < n_kitems && h >= 0 && h < H;
                 float acc[KD][VK];
 #pragma unroll
                 for (int v = 0; v < VK; ++v) acc[0][v] = 0.0f;
-                k_accumulate(row, strip, acc);
-                k_finish(row, strip, acc[KD - 1]);
+                if (ok) k_accumulate(row, strip, acc);
+                k_finish(ok ? row : -1, strip, acc[KD - 1]);
             }
         }
 
@@ -315,10 +365,17 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
             float zv[SCH][VA];
+            if (false) {
 #pragma unroll
-            for (int j = 0; j < SCH; ++j)
-                load_strip_global<T, VEC, VA>(zg + j * SP + (long long)d * HW + (long long)hrow * W,
-                                              w0, W, zv[j]);
+                for (int j = 0; j < SCH; ++j)
+#pragma unroll
+                    for (int v = 0; v < VA; ++v) zv[j][v] = zpre[j][v];
+            } else {
+#pragma unroll
+                for (int j = 0; j < SCH; ++j)
+                    load_strip_global<T, VEC, VA>(zg + j * SP + (long long)d * HW + (long long)hrow * W,
+                                                  w0, W, zv[j]);
+            }
             float an[SCH][VA], ad[SCH][VA];
 #pragma unroll
             for (int j = 0; j < SCH; ++j)

@@ -49,7 +49,7 @@ inline bool plan_fwd(int D, int H, int W, long long BC, Tiling& t, size_t& smem_
     const int NS8 = (t.NQ + 1) / 2;
     int TH = H;
     if (KD > 1) {
-        TH = std::min(TH, S::NT / NS8 - 2 * PH);                         // one K strip per thread
+        TH = std::min(TH, (S::NT / 2) / NS8 - 2 * PH);                   // one K strip per thread pair
         TH = std::min(TH, S::NT * S::MAXZ / (SCH * t.NQ) - 4 * PH);      // z prefetch registers
         TH = std::min(TH, S::NT * S::MAXX / t.NQ - 2 * PH);              // x prefetch registers
     }
