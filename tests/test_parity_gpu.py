@@ -142,6 +142,8 @@ RANDOM_CASES = [
     (256, 256, 4, (3, 3, 3), 2, (6, 5, 4)),
     (8, 8, 4, (3, 3, 3), 1, (20, 33, 70)),     # wider than one tile in every direction
     (4, 4, 4, (3, 3, 3), 1, (3, 40, 130)),
+    (2, 2, 4, (3, 3, 3), 1, (40, 12, 16)),     # deep and few slabs: several depth chunks per slab
+    (2, 2, 4, (3, 3, 3), 1, (37, 9, 20)),
     (6, 6, 4, (5, 5), 2, (70, 150)),
     (6, 6, 4, (3, 3), 2, (37, 41)),
     (4, 4, 4, (3, 3, 3), 2, (1, 1, 1)),        # degenerate extents
