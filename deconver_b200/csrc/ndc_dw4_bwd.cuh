@@ -75,8 +75,8 @@ __device__ __forceinline__ void cta_combine(float* scratch, const float (&acc)[N
     }
 }
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC>
-__global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, int WQ>
+__global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
     using L = RingSmem<KD, KH, KW>;
     constexpr int RING = L::RING;
@@ -84,7 +84,8 @@ __global__ void __launch_bounds__(NT, 2) ratio_kernel(const RatioParams P) {
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t, 2, 0);
     const int tid = threadIdx.x;
-    const int NQ = P.t.NQ, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch, H = P.H,
+              W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
     const long long HW = (long long)H * W, SP = HW * D;
 
     int blk = blockIdx.x;
@@ -286,7 +287,7 @@ struct KconvSmem {
 // 16-byte chunks land on 16-byte quads, and an 8-voxel strip reads a 4-quad window.
 // The KD running sums and their aux strips never move between registers: plane q lives in
 // slot q mod KD, and the step body exists in KD rotated copies.
-template <typename T, int KD, int KH, int KW, int NT, bool VEC, bool WGRAD>
+template <typename T, int KD, int KH, int KW, int NT, bool VEC, bool WGRAD, int WQ>
 __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = KconvSmem<KD, KH, KW>;
@@ -296,7 +297,8 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
     const int tid = threadIdx.x;
-    const int NQ = P.t.NQ, NS8 = (NQ + 1) / 2, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const int NQ = WQ ? WQ : P.t.NQ, NS8 = (NQ + 1) / 2, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch,
+              H = P.H, W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
     const long long HW = (long long)H * W, SP = HW * D;
     const int which = blockIdx.y;
 
@@ -553,7 +555,7 @@ struct GzParams {
     int relu;
 };
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD>
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD, int WQ>
 __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
     using L = RingSmem<KD, KH, KW>;
@@ -563,7 +565,8 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t, 1, NT);
     const int tid = threadIdx.x;
-    const int NQ = P.t.NQ, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch, H = P.H,
+              W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
     const long long HW = (long long)H * W, SP = HW * D;
 
     int blk = blockIdx.x;

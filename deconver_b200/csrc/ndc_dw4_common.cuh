@@ -35,10 +35,8 @@ struct Tiling {
 
 // floats per shared row: the data quads, one quad of left margin, and enough on the right for
 // the last strip's window (3 quads past an 8-strip start, rounded to an even quad count)
-__host__ __device__ inline int row_pitch(int W) {
-    const int nq = (W + 3) / 4;
-    const int ns8 = (nq + 1) / 2;
-    return 4 * (2 * ns8 + 4);
+__host__ __device__ constexpr int row_pitch(int W) {
+    return 4 * (2 * (((W + 3) / 4 + 1) / 2) + 4);
 }
 
 template <bool SWZ> __device__ __forceinline__ int phys_quad(int quad) {

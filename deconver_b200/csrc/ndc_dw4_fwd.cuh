@@ -60,7 +60,7 @@ struct FwdSmem {
     }
 };
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXZ, int MAXX, int MINB, bool VEC>
+template <typename T, int KD, int KH, int KW, int NT, int MAXZ, int MAXX, int MINB, bool VEC, int WQ>
 __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = FwdSmem<KD, KH, KW>;
@@ -69,7 +69,8 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
     const int tid = threadIdx.x;
-    const int NQ = P.t.NQ, NS8 = (NQ + 1) / 2, pitch = P.t.pitch, H = P.H, W = P.W, D = P.D;
+    const int NQ = WQ ? WQ : P.t.NQ, NS8 = (NQ + 1) / 2, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch,
+              H = P.H, W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
     const long long HW = (long long)H * W, SP = HW * D;
 
     // ---- which work item

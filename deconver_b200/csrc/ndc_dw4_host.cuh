@@ -70,10 +70,10 @@ inline bool aligned_for_vec(const void* p, int dtype) {
     return ((uintptr_t)p % (dtype == NDC_BF16 ? 8 : 16)) == 0;
 }
 
-template <typename T, int KD, int KH, int KW, bool VEC>
+template <typename T, int KD, int KH, int KW, bool VEC, int WQ>
 cudaError_t launch_fwd(const FwdParams& P, size_t smem_bytes, long long BC, cudaStream_t st) {
     using S = FwdShape<KD, KH, KW>;
-    auto kern = fwd_kernel<T, KD, KH, KW, S::NT, S::MAXZ, S::MAXX, S::MINB, VEC>;
+    auto kern = fwd_kernel<T, KD, KH, KW, S::NT, S::MAXZ, S::MAXX, S::MINB, VEC, WQ>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem_bytes);
     if (e != cudaSuccess) return e;
@@ -97,13 +97,15 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
     P.eps = g.eps; P.relu = g.relu;
     const bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
                      aligned_for_vec(out, dtype) && aligned_for_vec(t1, dtype);
-    return vec ? launch_fwd<T, KD, KH, KW, true>(P, smem, BC, st)
-               : launch_fwd<T, KD, KH, KW, false>(P, smem, BC, st);
+    // widths that occur in the published configurations get kernels with a compile-time width
+    if (vec && KD > 1 && g.W == 64) return launch_fwd<T, KD, KH, KW, true, 16>(P, smem, BC, st);
+    return vec ? launch_fwd<T, KD, KH, KW, true, 0>(P, smem, BC, st)
+               : launch_fwd<T, KD, KH, KW, false, 0>(P, smem, BC, st);
 }
 
 // ---------------------------------------------------------------------------- backward
 
-constexpr int kRatioNT = 256;   // ratio_kernel threads
+constexpr int kRatioNT = 128;   // ratio_kernel threads
 constexpr int kRatioMAXX = 2;   // its prefetch registers (quads) per tensor
 constexpr int kRingNT = 128;    // gz_kernel threads
 constexpr int kRingMAXX = 4;
@@ -112,7 +114,8 @@ constexpr int kKconvNT = 192;   // 48 strip slots x 4 channel lanes
 // Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
 template <int KD, int KH, int KW>
 inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, int maxx,
-                      int red_threads, size_t extra_bytes, Tiling& t, size_t& smem_bytes) {
+                      int red_threads, size_t extra_bytes, size_t smem_target, Tiling& t,
+                      size_t& smem_bytes) {
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
     t.NQ = (W + 3) / 4;
@@ -124,7 +127,7 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
         return (size_t)RingSmem<KD, KH, KW>(q, ntensors, red_threads).total_floats * sizeof(float) +
                extra_bytes;
     };
-    while (TH > 1 && (bytes(TH) > kSmemTwoPerSM || (TH + 2 * PH) * t.pitch > 65535)) --TH;
+    while (TH > 1 && (bytes(TH) > smem_target || (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
     t.nth = (H + TH - 1) / TH;
     t.TH = (H + t.nth - 1) / t.nth;
@@ -167,12 +170,12 @@ struct BwdPlan {
 template <int KD, int KH, int KW>
 inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     const long long BC = (long long)g.B * g.G;
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, kRatioNT, kRatioMAXX, 0, 0, p.ratio, p.smem_ratio))
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, kRatioNT, kRatioMAXX, 0, 0, 56 * 1024, p.ratio, p.smem_ratio))
         return false;
     if (!plan_kconv<KD, KH, KW>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
     // gz_kernel also stages two sets of 8 strips per thread (z and the direct term)
     if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, kRingNT, kRingMAXX, kRingNT,
-                               (size_t)2 * 2 * SCH * kRingNT * 16, p.gz, p.smem_gz))
+                               (size_t)2 * 2 * SCH * kRingNT * 16, kSmemTwoPerSM, p.gz, p.smem_gz))
         return false;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t src = (size_t)BC * SCH * g.SP * sizeof(float);
@@ -211,7 +214,7 @@ inline cudaError_t set_smem(K kern, size_t bytes) {
         if (_e != cudaSuccess) return _e;       \
     } while (0)
 
-template <typename T, int KD, int KH, int KW, bool VEC>
+template <typename T, int KD, int KH, int KW, bool VEC, int WQ>
 cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                             const float* h, const float* bias, const T* gout, T* gx, T* gz,
                             float* gh, float* gb, void* ws, cudaStream_t st) {
@@ -227,7 +230,7 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;
         P.gnum = gnum; P.gden = gden; P.gz = gz;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.ratio; P.eps = g.eps; P.relu = g.relu;
-        auto kern = ratio_kernel<T, KD, KH, KW, kRatioNT, kRatioMAXX, VEC>;
+        auto kern = ratio_kernel<T, KD, KH, KW, kRatioNT, kRatioMAXX, VEC, WQ>;
         NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
         kern<<<(unsigned)p.n_ratio, kRatioNT, p.smem_ratio, st>>>(P);
         launched();
@@ -253,11 +256,11 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         if (n > 0) {
             dim3 grid((unsigned)p.n_kconv, n);
             if (gh) {
-                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, true>;
+                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, true, WQ>;
                 NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
                 kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
             } else {
-                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, false>;
+                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, false, WQ>;
                 NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
                 kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
             }
@@ -269,11 +272,11 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.gt1 = gt1; P.z = z; P.gz = gz; P.h = h; P.bias = bias; P.partial = pb;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.gz; P.relu = g.relu;
         if (gh) {
-            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, true>;
+            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, true, WQ>;
             NDC_CUDA_TRY(set_smem(kern, p.smem_gz));
             kern<<<(unsigned)p.n_gz, kRingNT, p.smem_gz, st>>>(P);
         } else {
-            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, false>;
+            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, false, WQ>;
             NDC_CUDA_TRY(set_smem(kern, p.smem_gz));
             kern<<<(unsigned)p.n_gz, kRingNT, p.smem_gz, st>>>(P);
         }
@@ -302,8 +305,10 @@ cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* 
                aligned_for_vec(t1, dtype) && aligned_for_vec(gout, dtype);
     if (gx) vec = vec && aligned_for_vec(gx, dtype);
     if (gz) vec = vec && aligned_for_vec(gz, dtype);
-    return vec ? backward_launch<T, KD, KH, KW, true>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
-               : backward_launch<T, KD, KH, KW, false>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+    if (vec && KD > 1 && g.W == 64)
+        return backward_launch<T, KD, KH, KW, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+    return vec ? backward_launch<T, KD, KH, KW, true, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
+               : backward_launch<T, KD, KH, KW, false, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
 }
 
 template <typename T>
