@@ -459,10 +459,12 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
         for (int a = 0; a < KD; ++a)
 #pragma unroll
             for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
-        auto aux_strip = [&](int q, float (&dst)[VK]) {   // strip of plane q, zero outside the chunk
+        // strip of plane q of the aux tensor, zero outside the chunk; the row/column part of the
+        // address is fixed per thread
+        const T* aux_row = WGRAD ? auxg + (long long)(h0 + k_row) * W : nullptr;
+        auto aux_strip = [&](int q, float (&dst)[VK]) {
             if (k_ok && q >= d0 && q < d1)
-                load_strip_global<T, VEC, VK>(auxg + (long long)q * HW + (long long)(h0 + k_row) * W,
-                                              VK * k_strip, W, dst);
+                load_strip_global<T, VEC, VK>(aux_row + (long long)q * HW, VK * k_strip, W, dst);
             else {
 #pragma unroll
                 for (int v = 0; v < VK; ++v) dst[v] = 0.0f;
