@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
     const int items = TH * NQ;
     for (int d = d0; d < d1; ++d) {
         // prefetch the plane the next step needs
-        float4 xr[MAXX], tr[MAXX];
+        Raw4<T> xr[MAXX], tr[MAXX];
         const int qn = d + PD + 1;
         const bool have = KD > 1 && d + 1 < d1 && qn < D;
         if (have) {
@@ -154,8 +154,8 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
                 if (id < nx) {
                     const ChunkDesc dsc = desc[id];
                     if (dsc.goff >= 0) {
-                        xr[i] = load4<T, VEC>(xg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
-                        tr[i] = load4<T, VEC>(tg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
+                        xr[i] = load4_raw<T, VEC>(xg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
+                        tr[i] = load4_raw<T, VEC>(tg + (long long)qn * HW + dsc.goff, desc_n(dsc.soff));
                     }
                 }
             }
@@ -166,11 +166,11 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
             const int hrow = h0 + a_row, w0 = VA * a_q;
             const long long off = (long long)d * HW + (long long)hrow * W;
             // global strips first: their latency hides behind the tap sweep
-            float zv[SCH][VA], gv[SCH][VA];
+            Raw4<T> zraw[SCH], graw[SCH];   // converted in the epilogue
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                load_strip_global<T, VEC, VA>(zg + j * SP + off, w0, W, zv[j]);
-                load_strip_global<T, VEC, VA>(gg + j * SP + off, w0, W, gv[j]);
+                zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + off, w0, W);
+                graw[j] = load_strip_raw<T, VEC>(gg + j * SP + off, w0, W);
             }
             float an[SCH][VA], ad[SCH][VA];
 #pragma unroll
@@ -206,13 +206,15 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
             // epilogue: gnum, gden, direct term (an/ad are overwritten with gnum/gden)
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                float dv[VA];
+                float dv[VA], zj[VA], gj[VA];
+                raw_to_array(zraw[j], zj);
+                raw_to_array(graw[j], gj);
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
-                    float s = zv[j][v] + bj[j];
+                    float s = zj[v] + bj[j];
                     if (P.relu) s = fmaxf(s, 0.0f);
                     const float r = fast_div(1.0f, ad[j][v]);
-                    const float gr = gv[j][v] * r;
+                    const float gr = gj[v] * r;
                     const float gn = gr * s;
                     dv[v] = gr * an[j][v];
                     ad[j][v] = -(gn * an[j][v]) * r;
@@ -231,8 +233,8 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
                 if (id < nx) {
                     const ChunkDesc dsc = desc[id];
                     if (dsc.goff >= 0) {
-                        stage_chunk<PW, false>(xring + slot_of(qn) * lay.plane_t, dsc.soff, xr[i]);
-                        stage_chunk<PW, false>(tring + slot_of(qn) * lay.plane_t, dsc.soff, tr[i]);
+                        stage_chunk<PW, false>(xring + slot_of(qn) * lay.plane_t, dsc.soff, to_float4(xr[i]));
+                        stage_chunk<PW, false>(tring + slot_of(qn) * lay.plane_t, dsc.soff, to_float4(tr[i]));
                     }
                 }
             }
@@ -462,13 +464,20 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
         // strip of plane q of the aux tensor, zero outside the chunk; the row/column part of the
         // address is fixed per thread
         const T* aux_row = WGRAD ? auxg + (long long)(h0 + k_row) * W : nullptr;
-        auto aux_strip = [&](int q, float (&dst)[VK]) {
-            if (k_ok && q >= d0 && q < d1)
-                load_strip_global<T, VEC, VK>(aux_row + (long long)q * HW, VK * k_strip, W, dst);
-            else {
-#pragma unroll
-                for (int v = 0; v < VK; ++v) dst[v] = 0.0f;
+        auto aux_raw = [&](int q, Raw4<T> (&dst)[2]) {
+            if (k_ok && q >= d0 && q < d1) {
+                dst[0] = load_strip_raw<T, VEC>(aux_row + (long long)q * HW, VK * k_strip, W);
+                dst[1] = load_strip_raw<T, VEC>(aux_row + (long long)q * HW, VK * k_strip + 4, W);
+            } else {
+                dst[0].v = {}; dst[1].v = {};
             }
+        };
+        auto aux_strip = [&](int q, float (&dst)[VK]) {
+            Raw4<T> raw[2];
+            aux_raw(q, raw);
+            const float4 a = to_float4(raw[0]), b = to_float4(raw[1]);
+            dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+            dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
         };
         // plane q lives in slot (q - p_first) mod KD: at the first step (rotation 0) output plane
         // p_first + PD - kd is slot (PD - kd) mod KD
@@ -479,17 +488,20 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
         auto step = [&](auto rot, int p) {
             constexpr int R = decltype(rot)::value;
             constexpr int DONE = (R - PD + 2 * KD) % KD;     // slot of plane p-PD, reused for p+1+PD
-            float aux_next[VK];
-            if (WGRAD) aux_strip(p + 1 + PD, aux_next);
+            Raw4<T> aux_next[2];   // converted when it replaces the finished plane's strip
+            if (WGRAD) aux_raw(p + 1 + PD, aux_next);
             const bool have = p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
             if (have) copy_plane(p + 1);
             const int qdone = p - PD;
             if (k_ok && p >= 0 && p < D) accumulate(rot, p, k_row, k_strip, kacc, auxs);
             if (qdone >= d0 && qdone < d1) finish(qdone, k_ok ? k_row : -1, k_strip, kacc[DONE]);
 #pragma unroll
-            for (int v = 0; v < VK; ++v) {
-                kacc[DONE][v] = 0.0f;
-                if (WGRAD) auxs[WGRAD ? DONE : 0][v] = aux_next[v];
+            for (int v = 0; v < VK; ++v) kacc[DONE][v] = 0.0f;
+            if (WGRAD) {
+                const float4 a = to_float4(aux_next[0]), b = to_float4(aux_next[1]);
+                float (&dst)[VK] = auxs[WGRAD ? DONE : 0];
+                dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+                dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
             }
             if (VEC) cp_async_wait_all();
             __syncthreads();

@@ -102,6 +102,53 @@ __device__ __forceinline__ float4 load4<__nv_bfloat16, false>(const __nv_bfloat1
     return r;
 }
 
+// The same four elements as they sit in memory.  Loads that are issued early (prefetch, top of
+// an item) keep the raw form and convert where the values are used: a conversion right after
+// the load would make the warp wait for the memory there.
+template <typename T> struct Raw4;
+template <> struct Raw4<float> { float4 v; };
+template <> struct Raw4<__nv_bfloat16> { uint2 v; };
+
+__device__ __forceinline__ float4 to_float4(const Raw4<float>& r) { return r.v; }
+__device__ __forceinline__ float4 to_float4(const Raw4<__nv_bfloat16>& r) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T, bool VEC>
+__device__ __forceinline__ Raw4<T> load4_raw(const T* p, int n);
+template <>
+__device__ __forceinline__ Raw4<float> load4_raw<float, true>(const float* p, int) {
+    Raw4<float> r; r.v = __ldg(reinterpret_cast<const float4*>(p)); return r;
+}
+template <>
+__device__ __forceinline__ Raw4<float> load4_raw<float, false>(const float* p, int n) {
+    Raw4<float> r; r.v = load4<float, false>(p, n); return r;
+}
+template <>
+__device__ __forceinline__ Raw4<__nv_bfloat16> load4_raw<__nv_bfloat16, true>(const __nv_bfloat16* p, int) {
+    Raw4<__nv_bfloat16> r; r.v = __ldg(reinterpret_cast<const uint2*>(p)); return r;
+}
+template <>
+__device__ __forceinline__ Raw4<__nv_bfloat16> load4_raw<__nv_bfloat16, false>(const __nv_bfloat16* p, int n) {
+    const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
+    unsigned e0 = q[0], e1 = n > 1 ? q[1] : 0u, e2 = n > 2 ? q[2] : 0u, e3 = n > 3 ? q[3] : 0u;
+    Raw4<__nv_bfloat16> r; r.v = make_uint2(e0 | (e1 << 16), e2 | (e3 << 16)); return r;
+}
+// four voxels of a global row from column w0 (zero past the end of the row), raw
+template <typename T, bool VEC>
+__device__ __forceinline__ Raw4<T> load_strip_raw(const T* row, int w0, int W) {
+    const int n = W - w0;
+    if (n > 0) return load4_raw<T, VEC>(row + w0, n < 4 ? n : 4);
+    Raw4<T> r; r.v = {}; return r;
+}
+template <typename T>
+__device__ __forceinline__ void raw_to_array(const Raw4<T>& r, float (&v)[4]) {
+    const float4 t = to_float4(r);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+
 template <typename T, bool VEC>
 __device__ __forceinline__ void store4(T* p, int n, float4 v);
 

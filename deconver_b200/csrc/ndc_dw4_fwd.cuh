@@ -168,18 +168,18 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         }
         return v;
     };
-    auto fetch_z = [&](float4 (&reg)[MAXZ], int plane) {
+    auto fetch_z = [&](Raw4<T> (&reg)[MAXZ], int plane) {
         const T* src = zg + (long long)plane * HW;
 #pragma unroll
         for (int i = 0; i < MAXZ; ++i) {
             const int id = tid + i * NT;
             if (id < nz) {
                 const ChunkDesc dsc = zdesc[id];
-                if (dsc.goff >= 0) reg[i] = load4<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
+                if (dsc.goff >= 0) reg[i] = load4_raw<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
             }
         }
     };
-    auto stage_z = [&](const float4 (&reg)[MAXZ], int plane) {
+    auto stage_z = [&](const Raw4<T> (&reg)[MAXZ], int plane) {
         float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
 #pragma unroll
         for (int i = 0; i < MAXZ; ++i) {
@@ -187,29 +187,29 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             if (id < nz) {
                 const ChunkDesc dsc = zdesc[id];
                 if (dsc.goff >= 0)
-                    *reinterpret_cast<float4*>(dst + (dsc.soff & 0x3ffffff)) = rectify(reg[i], dsc.soff);
+                    *reinterpret_cast<float4*>(dst + (dsc.soff & 0x3ffffff)) = rectify(to_float4(reg[i]), dsc.soff);
             }
         }
     };
-    auto fetch_x = [&](float4 (&reg)[MAXX], int plane) {
+    auto fetch_x = [&](Raw4<T> (&reg)[MAXX], int plane) {
         const T* src = xg + (long long)plane * HW;
 #pragma unroll
         for (int i = 0; i < MAXX; ++i) {
             const int id = tid + i * NT;
             if (id < nx) {
                 const ChunkDesc dsc = xdesc[id];
-                if (dsc.goff >= 0) reg[i] = load4<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
+                if (dsc.goff >= 0) reg[i] = load4_raw<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
             }
         }
     };
-    auto stage_x = [&](const float4 (&reg)[MAXX], int slot) {
+    auto stage_x = [&](const Raw4<T> (&reg)[MAXX], int slot) {
         float* dst = xring + slot * lay.plane_t;
 #pragma unroll
         for (int i = 0; i < MAXX; ++i) {
             const int id = tid + i * NT;
             if (id < nx) {
                 const ChunkDesc dsc = xdesc[id];
-                if (dsc.goff >= 0) stage_chunk<PW, false>(dst, dsc.soff, reg[i]);
+                if (dsc.goff >= 0) stage_chunk<PW, false>(dst, dsc.soff, to_float4(reg[i]));
             }
         }
     };
@@ -249,23 +249,12 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
 
     for (int p = p_first; p <= p_last; ++p) {
         // -------- prefetch (global loads stay in flight during the K phase)
-        float4 zr[MAXZ], xr[MAXX];
+        Raw4<T> zr[MAXZ], xr[MAXX];
         const bool have_z = KD > 1 && p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
         const int xq = p - PD;
         const bool have_x = KD > 1 && xq >= 0 && xq < D && xq >= d0 - PD && xq <= d1 - 1 + PD;
         if (have_z) fetch_z(zr, p + 1);
         if (have_x) fetch_x(xr, xq);
-        // z of this thread's first A strip of this step: requested now, used after the K phase
-        float zpre[SCH][VA];
-        const int d_now = p - 2 * PD;
-        const bool a_now = false && d_now >= d0 && d_now < d1 && tid < a_items;
-        if (a_now) {
-#pragma unroll
-            for (int j = 0; j < SCH; ++j)
-                load_strip_global<T, VEC, VA>(zg + j * SP + (long long)d_now * HW +
-                                                  (long long)(h0 + tid / NQ) * W,
-                                              VA * (tid % NQ), W, zpre[j]);
-        }
 
         // -------- K phase: source plane p feeds t1 planes p+PD-kd
         const bool s_ok = p >= 0 && p < D;
@@ -365,18 +354,10 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         for (int item = tid; item < a_items; item += NT) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
-            float zv[SCH][VA];
-            if (false) {
+            Raw4<T> zraw[SCH];   // converted in the epilogue, after the tap sweep
 #pragma unroll
-                for (int j = 0; j < SCH; ++j)
-#pragma unroll
-                    for (int v = 0; v < VA; ++v) zv[j][v] = zpre[j][v];
-            } else {
-#pragma unroll
-                for (int j = 0; j < SCH; ++j)
-                    load_strip_global<T, VEC, VA>(zg + j * SP + (long long)d * HW + (long long)hrow * W,
-                                                  w0, W, zv[j]);
-            }
+            for (int j = 0; j < SCH; ++j)
+                zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + (long long)d * HW + (long long)hrow * W, w0, W);
             float an[SCH][VA], ad[SCH][VA];
 #pragma unroll
             for (int j = 0; j < SCH; ++j)
@@ -410,10 +391,11 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             }
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                float ov[VA];
+                float ov[VA], zj[VA];
+                raw_to_array(zraw[j], zj);
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
-                    float s = zv[j][v] + bj[j];
+                    float s = zj[v] + bj[j];
                     if (P.relu) s = fmaxf(s, 0.0f);
                     ov[v] = fast_div(s * an[j][v], ad[j][v]);
                 }
