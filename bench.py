@@ -265,22 +265,55 @@ def run_b200(args):
     gx_host = torch.empty(B, C, *S).pin_memory()
     grads_host = torch.empty_like(bucket.flat, device="cpu").pin_memory()
 
+    # Every step copies its own inputs in and its own results out; the copies of neighbouring
+    # steps overlap with compute on separate streams (device input buffers are double-buffered).
+    s_main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    x_dev = [torch.empty(B, C, *S, device=dev) for _ in range(2)]
+    g_dev = [torch.empty(B, C * r, *S, device=dev) for _ in range(2)]
+    in_done = [torch.cuda.Event() for _ in range(2)]
+    comp_done = [torch.cuda.Event() for _ in range(2)]
+    grads_out = torch.cuda.Event()
+    out_done = torch.cuda.Event()
+    state = {"i": 0}
+
     def e2e_step():
-        xd = x_host.to(dev, non_blocking=True).requires_grad_(True)
-        gd = g_host.to(dev, non_blocking=True)
-        y = step(xd, gd)
-        y_host.copy_(y.detach(), non_blocking=True)
-        gx_host.copy_(xd.grad, non_blocking=True)
-        grads_host.copy_(bucket.flat, non_blocking=True)
+        i = state["i"]
+        b = i % 2
+        state["i"] = i + 1
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(comp_done[b])       # the step that last used this buffer is done
+            x_dev[b].copy_(x_host, non_blocking=True)
+            g_dev[b].copy_(g_host, non_blocking=True)
+            in_done[b].record(s_in)
+        s_main.wait_event(in_done[b])
+        if i >= 1:
+            s_main.wait_event(grads_out)            # the bucket was read out before it is zeroed
+        xd = x_dev[b].detach().requires_grad_(True)
+        y = step(xd, g_dev[b])
+        gx = xd.grad
+        comp_done[b].record(s_main)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(comp_done[b])
+            grads_host.copy_(bucket.flat, non_blocking=True)
+            grads_out.record(s_out)
+            y_host.copy_(y.detach(), non_blocking=True)
+            gx_host.copy_(gx, non_blocking=True)
+            out_done.record(s_out)
+        y.record_stream(s_out)
+        gx.record_stream(s_out)
 
     for _ in range(2):
         e2e_step()
+    s_main.wait_event(out_done)
     barrier()
     e2e_steps = max(1, min(args.steps, 10))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    s_main.wait_event(out_done)                     # the last step's results are on the host
     e1.record()
     barrier()
     te = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)

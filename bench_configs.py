@@ -191,7 +191,7 @@ def config_4(dc, args):
     model = model.to(device=dev, dtype=torch.bfloat16).train()
     sl = shard_batch(16, rank, world)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
-    nb = sl.stop - sl.start
+    nb = args.per_gpu_batch or (sl.stop - sl.start)
     x = torch.rand(nb, 2, 64, 64, 64, device=dev, generator=gen).to(torch.bfloat16)
     y = (torch.rand(nb, 1, 64, 64, 64, device=dev, generator=gen) < 0.05).to(torch.bfloat16)
     params = [p for p in model.parameters() if p.requires_grad]
@@ -279,6 +279,8 @@ def main():
     ap.add_argument("--config", required=True, choices=["triton", "2", "4", "5"])
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--chunk", type=int, default=4)
+    ap.add_argument("--per-gpu-batch", type=int, default=0,
+                    help="config 4: override the per-GPU batch (single-GPU experiments)")
     args = ap.parse_args()
     dc = load_reference()
     if dc is None:

@@ -260,7 +260,7 @@ template <int KD, int KH, int KW>
 struct KconvSmem {
     static constexpr int PD = KD / 2, PH = KH / 2;
     static constexpr int WKP = (KD * KW + 3) / 4 * 4;
-    static constexpr int NSB = KD > 1 ? 2 : 1;
+    static constexpr int NSB = KD > 1 ? 3 : 1;   // planes p, p+1 (landed) and p+2 (in flight)
     int wK, sbuf, desc, total_floats, RS, plane_s;
     __host__ __device__ KconvSmem(const Tiling& t) {
         RS = t.TH + 2 * PH;
@@ -352,10 +352,11 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
     for (int k = 0; k < NW; ++k) accw[k] = 0.0f;
     __syncthreads();
 
+    const int p_first = d0 - PD, p_last = d1 - 1 + PD;
     // plane -> shared buffer: asynchronous 16-byte copies where rows allow, else through registers
     auto copy_plane = [&](int plane) {
         const float* src = ing + (long long)plane * HW;
-        float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
+        float* dst = sbuf + ((plane - p_first) % NSB) * lay.plane_s;
         for (int id = tid; id < nz; id += NT) {
             const ChunkDesc dsc = desc[id];
             if (dsc.goff < 0) continue;
@@ -369,12 +370,13 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
         }
         if (VEC) cp_async_commit();
     };
+    auto wait_but_newest = [&]() { if (VEC) asm volatile("cp.async.wait_group 1;\n" ::: "memory"); };
     // one source row of this thread's channel feeds KD output planes (and their correlations);
     // output plane p+PD-kd lives in slot (R + PD - kd) mod KD, R = rotation of this step
     auto accumulate = [&](auto rot, int p, int row, int strip, float (&acc)[KD][VK],
                           const float (&aux)[WGRAD ? KD : 1][VK]) {
         constexpr int R = decltype(rot)::value;
-        const float* sp = sbuf + (p & (NSB - 1)) * lay.plane_s + (jch * RS + row) * pitch;
+        const float* sp = sbuf + ((p - p_first) % NSB) * lay.plane_s + (jch * RS + row) * pitch;
         int qo[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) qo[q] = phys_quad<true>(2 * strip + q) << 2;
@@ -447,9 +449,12 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
         }
     };
 
-    const int p_first = d0 - PD, p_last = d1 - 1 + PD;
-    if (p_first >= 0 && p_first < D) copy_plane(p_first);
-    if (VEC) cp_async_wait_all();
+    // planes are requested two steps ahead of their use: a step is shorter than the memory
+    // latency under load
+    auto plane_ok = [&](int q) { return q >= 0 && q < D && q <= p_last; };
+    if (plane_ok(p_first)) copy_plane(p_first); else if (VEC) cp_async_commit();
+    if (KD > 1) { if (plane_ok(p_first + 1)) copy_plane(p_first + 1); else if (VEC) cp_async_commit(); }
+    if (KD > 1) wait_but_newest(); else if (VEC) cp_async_wait_all();
     __syncthreads();
 
     if (KD > 1) {
@@ -485,25 +490,27 @@ __global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd) aux_strip(p_first + PD - kd, auxs[WGRAD ? (PD - kd + KD) % KD : 0]);
         }
+        Raw4<T> aux_near[2];
+        if (WGRAD) aux_raw(p_first + 1 + PD, aux_near); else { aux_near[0].v = {}; aux_near[1].v = {}; }
         auto step = [&](auto rot, int p) {
             constexpr int R = decltype(rot)::value;
             constexpr int DONE = (R - PD + 2 * KD) % KD;     // slot of plane p-PD, reused for p+1+PD
-            Raw4<T> aux_next[2];   // converted when it replaces the finished plane's strip
-            if (WGRAD) aux_raw(p + 1 + PD, aux_next);
-            const bool have = p + 1 <= p_last && p + 1 >= 0 && p + 1 < D;
-            if (have) copy_plane(p + 1);
+            Raw4<T> aux_far[2];   // aux strip two steps ahead (raw); aux_near is next step's
+            if (WGRAD) aux_raw(p + 2 + PD, aux_far);
+            if (plane_ok(p + 2)) copy_plane(p + 2); else if (VEC) cp_async_commit();
             const int qdone = p - PD;
             if (k_ok && p >= 0 && p < D) accumulate(rot, p, k_row, k_strip, kacc, auxs);
             if (qdone >= d0 && qdone < d1) finish(qdone, k_ok ? k_row : -1, k_strip, kacc[DONE]);
 #pragma unroll
             for (int v = 0; v < VK; ++v) kacc[DONE][v] = 0.0f;
             if (WGRAD) {
-                const float4 a = to_float4(aux_next[0]), b = to_float4(aux_next[1]);
+                const float4 a = to_float4(aux_near[0]), b = to_float4(aux_near[1]);
                 float (&dst)[VK] = auxs[WGRAD ? DONE : 0];
                 dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
                 dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+                aux_near[0] = aux_far[0]; aux_near[1] = aux_far[1];
             }
-            if (VEC) cp_async_wait_all();
+            wait_but_newest();   // plane p+1 has landed; p+2 may still be in flight
             __syncthreads();
         };
         int p = p_first;

@@ -2,7 +2,6 @@
 #pragma once
 
 #include <algorithm>
-#include <cstdlib>
 
 #include "ndc_dw4_fwd.cuh"
 #include "ndc_dw4_bwd.cuh"
@@ -27,17 +26,7 @@ inline bool shape_supported(int kD, int kH, int kW) {
 
 // Chunks along depth: enough CTAs for about `waves` rounds of two CTAs per SM, but chunks of
 // at least 16 planes (every chunk recomputes 2*PD planes of its neighbours).
-inline int tune_env(const char* name) {   // tuning override for experiments; 0 = not set
-    const char* v = std::getenv(name);
-    return v ? std::atoi(v) : 0;
-}
-
 inline void plan_depth(int KD, int D, long long ctas_per_chunk, int waves, Tiling& t) {
-    if (KD > 1 && tune_env("NDC_TUNE_DC") > 0) {
-        t.DC = std::min(D, tune_env("NDC_TUNE_DC"));
-        t.ndc = (D + t.DC - 1) / t.DC;
-        return;
-    }
     if (KD == 1) {
         t.DC = 1;
     } else {
@@ -69,7 +58,6 @@ inline bool plan_fwd(int D, int H, int W, long long BC, Tiling& t, size_t& smem_
         return (size_t)FwdSmem<KD, KH, KW>(q).total_floats * sizeof(float);
     };
     while (TH > 1 && (bytes(TH) > kSmemTwoPerSM || SCH * (TH + 4 * PH) * t.pitch > 65535)) --TH;
-    if (tune_env("NDC_TUNE_TH_FWD") > 0) TH = std::min(TH, tune_env("NDC_TUNE_TH_FWD"));
     if (TH < 1 || bytes(TH) > kSmemMax || SCH * (TH + 4 * PH) * t.pitch > 65535) return false;
     t.nth = (H + TH - 1) / TH;
     t.TH = (H + t.nth - 1) / t.nth;
@@ -230,7 +218,6 @@ template <typename T, int KD, int KH, int KW, bool VEC, int WQ>
 cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                             const float* h, const float* bias, const T* gout, T* gx, T* gz,
                             float* gh, float* gb, void* ws, cudaStream_t st) {
-    const long long BC = (long long)g.B * g.G;
     float* gnum = (float*)((char*)ws + p.off_gnum);
     float* gden = (float*)((char*)ws + p.off_gden);
     float* gt1 = (float*)((char*)ws + p.off_gt1);
