@@ -54,8 +54,8 @@ struct FwdSmem {
         sbuf = o; o += NSB * plane_s;
         t1ring = o; o += RING * plane_t;
         xring = o; o += RING * plane_t;
-        zdesc = o; o += KD > 1 ? 2 * (SCH * RS * t.NQ) : 0;  // loader tables: marching kernels only
-        xdesc = o; o += KD > 1 ? 2 * (RT * t.NQ) : 0;
+        zdesc = o;                                    // (end of the zero-initialised area)
+        xdesc = o; o += KD > 1 ? 2 * (RT * t.NQ) : 0;  // x loader table: marching kernels only
         total_floats = o;
     }
 };
@@ -94,11 +94,11 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     float* sbuf = smem + lay.sbuf;
     float* t1ring = smem + lay.t1ring;
     float* xring = smem + lay.xring;
-    ChunkDesc* zdesc = reinterpret_cast<ChunkDesc*>(smem + lay.zdesc);
     ChunkDesc* xdesc = reinterpret_cast<ChunkDesc*>(smem + lay.xdesc);
 
     // ---- one-time set-up: zero the planes, stage the filter, build the loader tables
-    for (int i = tid; i < lay.zdesc - lay.sbuf; i += NT) sbuf[i] = 0.0f;
+    for (int i = tid; i < (lay.zdesc - lay.sbuf) / 4; i += NT)
+        reinterpret_cast<float4*>(sbuf)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     {
         const float* hc = P.h + (long long)c * SCH * (KD * KH * KW);
         for (int i = tid; i < KD * KH * KW * SCH; i += NT) {
@@ -121,20 +121,27 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     auto z_soff = [&](int ch, int r, int c4, int n) {
         return ((ch * RS + r) * pitch + (phys_quad<true>(c4 + 1) << 2)) | (n << 26) | (ch << 29);
     };
-    if (KD > 1) {
-        for (int id = tid; id < nz; id += NT) {
-            const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
-            const int h = h0 - 2 * PH + r, w = 4 * c4;
-            ChunkDesc dsc;
-            dsc.goff = (h < 0 || h >= H) ? -1 : (int)(ch * SP) + h * W + w;
-            dsc.soff = z_soff(ch, r, c4, min(4, W - w));
-            zdesc[id] = dsc;
-        }
-        build_descs(xdesc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
-    }
+    if (KD > 1) build_descs(xdesc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
+
+    // ---- this thread's chunks of a z plane (fixed for the CTA's lifetime, kept in registers):
+    // element offset in the plane (-1: nothing to load), shared offset | valid count, bias
+    int zg_off[MAXZ], zs_off[MAXZ];
+    float zb[MAXZ];
+#pragma unroll
+    for (int i = 0; i < MAXZ; ++i) {
+        const int id = tid + i * NT;
+        zg_off[i] = -1; zs_off[i] = 0; zb[i] = 0.0f;
+        if (KD > 1 && id < nz) {
+            const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
+            const int h = h0 - 2 * PH + r, w = 4 * c4;
+            if (h >= 0 && h < H) zg_off[i] = (int)(ch * SP) + h * W + w;
+            zs_off[i] = z_soff(ch, r, c4, min(4, W - w));
+            zb[i] = ch == 0 ? bj[0] : ch == 1 ? bj[1] : ch == 2 ? bj[2] : bj[3];
+        }
+    }
 
     // ---- this thread's K strip (8 voxels of one row of the t1 band), its channel pair and
     // its partial running sums.  lane = pair*16 + strip lane: a quarter-warp reads 8
@@ -153,15 +160,13 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     const int a_items = TH * NQ;
     __syncthreads();
 
-    auto rectify = [&](float4 v, int soff) {
-        const int j = desc_ch(soff), n = desc_n(soff);
-        const float b = j == 0 ? bj[0] : j == 1 ? bj[1] : j == 2 ? bj[2] : bj[3];
+    auto rectify = [&](float4 v, float b, int n) {
         v.x += b; v.y += b; v.z += b; v.w += b;
         if (P.relu) {
             v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f);
             v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
         }
-        if (n < 4) {  // elements past the end of the row stay zero
+        if (!VEC && n < 4) {  // elements past the end of the row stay zero
             if (n < 2) v.y = 0.f;
             if (n < 3) v.z = 0.f;
             v.w = 0.f;
@@ -171,25 +176,16 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     auto fetch_z = [&](Raw4<T> (&reg)[MAXZ], int plane) {
         const T* src = zg + (long long)plane * HW;
 #pragma unroll
-        for (int i = 0; i < MAXZ; ++i) {
-            const int id = tid + i * NT;
-            if (id < nz) {
-                const ChunkDesc dsc = zdesc[id];
-                if (dsc.goff >= 0) reg[i] = load4_raw<T, VEC>(src + dsc.goff, desc_n(dsc.soff));
-            }
-        }
+        for (int i = 0; i < MAXZ; ++i)
+            if (zg_off[i] >= 0) reg[i] = load4_raw<T, VEC>(src + zg_off[i], (zs_off[i] >> 26) & 7);
     };
     auto stage_z = [&](const Raw4<T> (&reg)[MAXZ], int plane) {
         float* dst = sbuf + (plane & (NSB - 1)) * lay.plane_s;
 #pragma unroll
-        for (int i = 0; i < MAXZ; ++i) {
-            const int id = tid + i * NT;
-            if (id < nz) {
-                const ChunkDesc dsc = zdesc[id];
-                if (dsc.goff >= 0)
-                    *reinterpret_cast<float4*>(dst + (dsc.soff & 0x3ffffff)) = rectify(to_float4(reg[i]), dsc.soff);
-            }
-        }
+        for (int i = 0; i < MAXZ; ++i)
+            if (zg_off[i] >= 0)
+                *reinterpret_cast<float4*>(dst + (zs_off[i] & 0x3ffffff)) =
+                    rectify(to_float4(reg[i]), zb[i], (zs_off[i] >> 26) & 7);
     };
     auto fetch_x = [&](Raw4<T> (&reg)[MAXX], int plane) {
         const T* src = xg + (long long)plane * HW;
@@ -224,7 +220,8 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             if (h < 0 || h >= H) continue;
             const int soff = z_soff(ch, r, c4, n);
             const float4 v = load4<T, VEC>(src + ch * SP + (long long)h * W + w, n);
-            *reinterpret_cast<float4*>(dst + (soff & 0x3ffffff)) = rectify(v, soff);
+            const float b = ch == 0 ? bj[0] : ch == 1 ? bj[1] : ch == 2 ? bj[2] : bj[3];
+            *reinterpret_cast<float4*>(dst + (soff & 0x3ffffff)) = rectify(v, b, n);
         }
     };
     auto load_x_now = [&](int plane, int slot) {
