@@ -315,3 +315,43 @@ def test_tiled_kernels_match_generic_kernels_at_full_size(dev, shape, dtype):
     for name, a, b in zip(("out", "gx", "gz", "gh", "gb"), res[1], res[0]):
         err = max_norm_error(a.float().cpu().numpy(), b.float().cpu().numpy())
         assert err < tol, f"{name} error {err:.3e}"
+
+
+def test_tiled_kernels_match_generic_kernels_on_random_geometries(dev):
+    """Seeded sweep over ragged shapes (band, chunk and strip tails of every kind): the tiled
+    depthwise kernels against the generic ones, forward and every gradient."""
+    rng = np.random.default_rng(2024)
+    cases = []
+    for _ in range(24):
+        if rng.random() < 0.6:
+            ks = (3, 3, 3)
+            spatial = (int(rng.integers(1, 45)), int(rng.integers(1, 40)), int(rng.integers(1, 75)))
+        else:
+            ks = (5, 5) if rng.random() < 0.5 else (3, 3)
+            spatial = (int(rng.integers(1, 90)), int(rng.integers(1, 200)))
+        cases.append((int(rng.integers(1, 3)), int(rng.integers(1, 5)), ks, spatial,
+                      bool(rng.random() < 0.7)))
+    cases += [(1, 2, (3, 3, 3), (70, 3, 8), True), (1, 1, (3, 3, 3), (5, 64, 64), True),
+              (1, 1, (5, 5), (64, 256), False), (2, 3, (3, 3), (33, 256), True)]
+    for B, C, ks, spatial, relu in cases:
+        gen = torch.Generator(device=dev).manual_seed(B * 1000 + C * 100 + sum(spatial))
+        x = torch.rand(B, C, *spatial, device=dev, generator=gen)
+        z = torch.randn(B, 4 * C, *spatial, device=dev, generator=gen) * 0.5 + 0.3
+        if not relu:
+            z = z.abs()
+        h = torch.rand(C, 4, *ks, device=dev, generator=gen) / float(np.prod(ks))
+        bias = torch.randn(4 * C, device=dev, generator=gen) * 0.1 if relu else None
+        gout = torch.randn(B, 4 * C, *spatial, device=dev, generator=gen)
+        cfg = dict(groups=C, m=1, sc=4, eps=1e-16, relu_input=relu)
+        res = []
+        for generic in (True, False):
+            t = [v.clone().requires_grad_(True) for v in (x, z, h)]
+            b = None if bias is None else bias.clone().requires_grad_(True)
+            with Fn.force_generic(generic):
+                out = dcb.deconv_update(t[0], t[1], t[2], b, **cfg)
+                out.backward(gout)
+            res.append([out.detach()] + [v.grad for v in t] + ([] if b is None else [b.grad]))
+        torch.cuda.synchronize()
+        for name, a, r in zip(("out", "gx", "gz", "gh", "gb"), res[1], res[0]):
+            err = max_norm_error(a.cpu().numpy(), r.cpu().numpy())
+            assert err < F32_TOL, f"{name} error {err:.3e} for B={B} C={C} k={ks} S={spatial} relu={relu}"
