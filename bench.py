@@ -394,6 +394,10 @@ def run_profile_case(args):
     dev = torch.device("cuda", 0)
     dcb.load_library()
     C, r, ks, S = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"], WORKLOAD["spatial"]
+    if args.channels:
+        C = args.channels
+    if args.size:
+        S = (args.size,) * 3
     B = args.batch
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     gen = torch.Generator(device=dev).manual_seed(0)
@@ -409,7 +413,8 @@ def run_profile_case(args):
         out.backward(g)
         x.grad = z.grad = h.grad = b.grad = None
     ms = Fn.timing.disable_and_collect()
-    print(json.dumps({"profile_case": True, "batch": B, "steps": args.steps, "dtype": args.dtype,
+    print(json.dumps({"profile_case": True, "batch": B, "channels": C, "spatial": list(S),
+                      "steps": args.steps, "dtype": args.dtype,
                       "ndc_fwd_ms": [round(v, 4) for v in ms["ndc_fwd"]],
                       "ndc_bwd_ms": [round(v, 4) for v in ms["ndc_bwd"]]}))
 
@@ -426,6 +431,8 @@ def main():
                     help="run only a few update calls at --batch (for an ncu capture)")
     ap.add_argument("--batch", type=int, default=1, help="batch of --profile-case")
     ap.add_argument("--dtype", choices=["f32", "bf16"], default="f32", help="dtype of --profile-case")
+    ap.add_argument("--channels", type=int, default=0, help="channels of --profile-case (default 64)")
+    ap.add_argument("--size", type=int, default=0, help="cubic extent of --profile-case (default 64)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)

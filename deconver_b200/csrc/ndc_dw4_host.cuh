@@ -98,7 +98,10 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
     const bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
                      aligned_for_vec(out, dtype) && aligned_for_vec(t1, dtype);
     // widths that occur in the published configurations get kernels with a compile-time width
-    if (vec && KD > 1 && g.W == 64) return launch_fwd<T, KD, KH, KW, true, 16>(P, smem, BC, st);
+    if constexpr (KD > 1) {
+        if (vec && g.W == 64) return launch_fwd<T, KD, KH, KW, true, 16>(P, smem, BC, st);
+        if (vec && g.W == 128) return launch_fwd<T, KD, KH, KW, true, 32>(P, smem, BC, st);
+    }
     return vec ? launch_fwd<T, KD, KH, KW, true, 0>(P, smem, BC, st)
                : launch_fwd<T, KD, KH, KW, false, 0>(P, smem, BC, st);
 }
@@ -304,8 +307,12 @@ cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* 
                aligned_for_vec(t1, dtype) && aligned_for_vec(gout, dtype);
     if (gx) vec = vec && aligned_for_vec(gx, dtype);
     if (gz) vec = vec && aligned_for_vec(gz, dtype);
-    if (vec && KD > 1 && g.W == 64)
-        return backward_launch<T, KD, KH, KW, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+    if constexpr (KD > 1) {
+        if (vec && g.W == 64)
+            return backward_launch<T, KD, KH, KW, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+        if (vec && g.W == 128)
+            return backward_launch<T, KD, KH, KW, true, 32>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+    }
     return vec ? backward_launch<T, KD, KH, KW, true, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
                : backward_launch<T, KD, KH, KW, false, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
 }
