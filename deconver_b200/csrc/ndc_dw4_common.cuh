@@ -2,16 +2,18 @@
 //
 // Work decomposition.  One CTA owns one (sample, group) pair, a band of TH rows spanning the
 // full width W, and a chunk of DC planes, and marches through the chunk plane by plane.
-// Planes live in shared memory as float32 rows of `pitch` floats.  Shared column c holds
-// w = c - (4 + PW), PW = kW/2: with that shift the inputs of a strip that starts at a
-// multiple of 4 begin on a 16-byte quad, so a strip's window is read as whole quads:
+// Planes live in shared memory as float32 rows of `pitch` floats, in one of two layouts:
 //
-//   A-type sweep (adjoint taps, many accumulators): strips of 4 voxels, window = 2 quads
-//   K-type sweep (rolling sums along depth, few accumulators): strips of 8, window = 3 quads
+//   ring rows (single-channel planes read by A-type sweeps: adjoint taps, many accumulators,
+//   strips of 4 voxels): shared column c holds w = c - (4 + PW), PW = kW/2.  With that shift
+//   the window of a strip that starts at a multiple of 4 begins on a 16-byte quad and is two
+//   quads long.  Consecutive lanes read consecutive quads, so these rows stay linear.
 //
-// Rows read by 8-voxel strips are XOR-swizzled at quad granularity (`SWZ`), so that the eight
-// lanes of a quarter-warp, two quads apart, hit eight distinct bank groups; rows read by
-// 4-voxel strips are consecutive quads already and stay linear.
+//   source rows (4-channel planes read by K-type sweeps: running sums along depth, strips of
+//   8 voxels): shared column c holds w = c - 4, so 16-byte chunks from HBM land on whole quads
+//   (vector stores, cp.async); a strip's window is the four quads 2k .. 2k+3.  The eight lanes
+//   of a quarter-warp are two quads apart, so quads are XOR-swizzled (`phys_quad<true>`) to hit
+//   eight distinct bank groups.
 #pragma once
 
 #include "ndc_common.cuh"

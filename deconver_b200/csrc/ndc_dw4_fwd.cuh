@@ -5,7 +5,8 @@
 // in ONE kernel.  t1 never makes a round trip through HBM: each CTA marches through its depth
 // chunk and keeps the planes it needs in shared-memory rings.  Per step p (a source plane):
 //
-//   prefetch   z plane p+1 and x plane p-PD into registers (global loads in flight)
+//   prefetch   z plane p+1 and x plane p-PD into registers, raw (global loads in flight;
+//              converted, biased and rectified only when they are staged)
 //   K phase    an 8-voxel strip of the t1 band (TH + 2*PH rows) is shared by two threads, each
 //              convolving two of the four source channels; each keeps KD partial running
 //              sums, one per t1 plane that source plane p contributes to; plane p-PD is
