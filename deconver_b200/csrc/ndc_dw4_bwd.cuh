@@ -172,11 +172,15 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
                 zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + off, w0, W);
                 graw[j] = load_strip_raw<T, VEC>(gg + j * SP + off, w0, W);
             }
-            float an[SCH][VA], ad[SCH][VA];
+            // accumulators hold channel pairs (2jp, 2jp+1) of one voxel
+            f32x2 an2[SCH / 2][VA], ad2[SCH / 2][VA];
+            {
+                const f32x2 e2 = pack2(P.eps, P.eps);
 #pragma unroll
-            for (int j = 0; j < SCH; ++j)
+                for (int jp = 0; jp < SCH / 2; ++jp)
 #pragma unroll
-                for (int v = 0; v < VA; ++v) { an[j][v] = P.eps; ad[j][v] = P.eps; }
+                    for (int v = 0; v < VA; ++v) { an2[jp][v] = e2; ad2[jp][v] = e2; }
+            }
 #pragma unroll 1
             for (int kd = 0; kd < KD; ++kd) {
                 const int q = d + PD - kd;
@@ -185,44 +189,32 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
 #pragma unroll
                 for (int kh = 0; kh < KH; ++kh) {
                     const int rr = a_row + PH + PH - kh;
-                    float xv[4 * NQA], tv[4 * NQA];
-                    load_window<NQA, false>(xring + slot * lay.plane_t + rr * pitch, a_q + 1, xv);
-                    load_window<NQA, false>(tring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
-#pragma unroll
-                    for (int kw = 0; kw < KW; ++kw) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(
-                            wA + ((kd * KH + kh) * KW + kw) * SCH);
-                        const float wj[SCH] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-                        for (int j = 0; j < SCH; ++j)
-#pragma unroll
-                            for (int v = 0; v < VA; ++v) {
-                                an[j][v] = fmaf(xv[v + 2 * PW - kw], wj[j], an[j][v]);
-                                ad[j][v] = fmaf(tv[v + 2 * PW - kw], wj[j], ad[j][v]);
-                            }
-                    }
+                    adjoint_row2<KW, NQA>(xring + slot * lay.plane_t + rr * pitch,
+                                          tring + slot * lay.plane_t + rr * pitch, a_q + 1,
+                                          wA + (kd * KH + kh) * KW * SCH, an2, ad2);
                 }
             }
-            // epilogue: gnum, gden, direct term (an/ad are overwritten with gnum/gden)
+            // epilogue: gnum, gden, direct term
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
-                float dv[VA], zj[VA], gj[VA];
+                float dv[VA], zj[VA], gj[VA], gnv[VA], gdv[VA];
                 raw_to_array(zraw[j], zj);
                 raw_to_array(graw[j], gj);
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
                     float s = zj[v] + bj[j];
                     if (P.relu) s = fmaxf(s, 0.0f);
-                    const float r = fast_div(1.0f, ad[j][v]);
+                    const float n = lane_of(an2[j / 2][v], j & 1);
+                    const float r = fast_div(1.0f, lane_of(ad2[j / 2][v], j & 1));
                     const float gr = gj[v] * r;
                     const float gn = gr * s;
-                    dv[v] = gr * an[j][v];
-                    ad[j][v] = -(gn * an[j][v]) * r;
-                    an[j][v] = gn;
-                    if (w0 + v >= W) { an[j][v] = 0.0f; ad[j][v] = 0.0f; }
+                    dv[v] = gr * n;
+                    gdv[v] = -(gn * n) * r;
+                    gnv[v] = gn;
+                    if (w0 + v >= W) { gnv[v] = 0.0f; gdv[v] = 0.0f; }
                 }
-                store_strip_global<float, VEC, VA>(gng + j * SP + off, w0, W, an[j]);
-                store_strip_global<float, VEC, VA>(gdg + j * SP + off, w0, W, ad[j]);
+                store_strip_global<float, VEC, VA>(gng + j * SP + off, w0, W, gnv);
+                store_strip_global<float, VEC, VA>(gdg + j * SP + off, w0, W, gdv);
                 if (dirg) store_strip_global<T, VEC, VA>(dirg + j * SP + off, w0, W, dv);
             }
         }
@@ -617,9 +609,14 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
-    float acc[NACC];   // [taps*4] filter-gradient sums (if WGRAD), then 4 bias sums
+    // filter-gradient sums [tap][channel pair] (if WGRAD), and 4 bias sums
+    constexpr int NW2 = (NACC - SCH) / 2 > 0 ? (NACC - SCH) / 2 : 1;
+    f32x2 acc2[NW2];
+    float gbs[SCH];
 #pragma unroll
-    for (int k = 0; k < NACC; ++k) acc[k] = 0.0f;
+    for (int k = 0; k < NW2; ++k) acc2[k] = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < SCH; ++j) gbs[j] = 0.0f;
     __syncthreads();
 
     const int qbase = d0 - PD - 1;
@@ -698,12 +695,17 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
                     if (w0 + v >= W) sv[j][v] = 0.0f;
                 }
             }
-            // the accumulators start from the direct term
-            float ag[SCH][VA];
+            // channel pairs (2jp, 2jp+1) of one voxel share a register pair; the accumulators
+            // start from the direct term
+            f32x2 ag[SCH / 2][VA], s2[SCH / 2][VA];
 #pragma unroll
-            for (int j = 0; j < SCH; ++j)
+            for (int jp = 0; jp < SCH / 2; ++jp)
 #pragma unroll
-                for (int v = 0; v < VA; ++v) ag[j][v] = gzg ? strips[SCH + j][v] : 0.0f;
+                for (int v = 0; v < VA; ++v) {
+                    ag[jp][v] = gzg ? pack2(strips[SCH + 2 * jp][v], strips[SCH + 2 * jp + 1][v])
+                                    : pack2(0.0f, 0.0f);
+                    s2[jp][v] = pack2(sv[2 * jp][v], sv[2 * jp + 1][v]);
+                }
 #pragma unroll
             for (int kd = 0; kd < KD; ++kd) {
                 const int q = d + PD - kd;
@@ -714,20 +716,24 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
                     const int rr = a_row + PH + PH - kh;
                     float tv[4 * NQA];
                     load_window<NQA, false>(ring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
+                    f32x2 t2[VA + KW - 1];
+#pragma unroll
+                    for (int i = 0; i < VA + KW - 1; ++i) t2[i] = pack2(tv[i], tv[i]);
 #pragma unroll
                     for (int kw = 0; kw < KW; ++kw) {
                         const float4 w4 = *reinterpret_cast<const float4*>(
                             wA + ((kd * KH + kh) * KW + kw) * SCH);
-                        const float wj[SCH] = {w4.x, w4.y, w4.z, w4.w};
+                        const f32x2 wp[SCH / 2] = {pack2(w4.x, w4.y), pack2(w4.z, w4.w)};
 #pragma unroll
-                        for (int j = 0; j < SCH; ++j) {
-                            float a = WGRAD ? acc[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] : 0.0f;
+                        for (int jp = 0; jp < SCH / 2; ++jp) {
+                            const int k2 = WGRAD ? ((kd * KH + kh) * KW + kw) * (SCH / 2) + jp : 0;
+                            f32x2 a = acc2[k2];
 #pragma unroll
                             for (int v = 0; v < VA; ++v) {
-                                ag[j][v] = fmaf(tv[v + 2 * PW - kw], wj[j], ag[j][v]);
-                                if (WGRAD) a = fmaf(sv[j][v], tv[v + 2 * PW - kw], a);
+                                fma2(ag[jp][v], t2[v + 2 * PW - kw], wp[jp]);
+                                if (WGRAD) fma2(a, s2[jp][v], t2[v + 2 * PW - kw]);
                             }
-                            if (WGRAD) acc[WGRAD ? ((kd * KH + kh) * KW + kw) * SCH + j : 0] = a;
+                            if (WGRAD) acc2[k2] = a;
                         }
                     }
                 }
@@ -738,12 +744,12 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
                     float dv[VA];
 #pragma unroll
                     for (int v = 0; v < VA; ++v) {
-                        float r = ag[j][v];
+                        float r = lane_of(ag[j / 2][v], j & 1);
                         if (P.relu && !(pre[j][v] > 0.0f)) r = 0.0f;
                         if (w0 + v >= W) r = 0.0f;
                         dv[v] = r;
                         // the bias gradient sums the values as stored (rounded to the storage type)
-                        acc[NACC - SCH + j] += to_f32(from_f32<T>(r));
+                        gbs[j] += to_f32(from_f32<T>(r));
                     }
                     store_strip_global<T, VEC, VA>(gzg + j * SP + off, w0, W, dv);
                 }
@@ -766,7 +772,9 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     constexpr int LD = NACC + 1;
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < NACC; ++k) ring[tid * LD + k] = acc[k];
+    for (int k = 0; k < NACC - SCH; ++k) ring[tid * LD + k] = lane_of(acc2[k / 2], k & 1);
+#pragma unroll
+    for (int j = 0; j < SCH; ++j) ring[tid * LD + NACC - SCH + j] = gbs[j];
     __syncthreads();
     for (int k = tid; k < NACC; k += NT) {
         float s = 0.0f;

@@ -305,6 +305,61 @@ struct StripFetcher {
     }
 };
 
+// Two float32 lanes in one 64-bit register, for `fma.rn.f32x2`: one issue slot for two
+// fused multiply-adds, each rounded exactly like `fmaf`.  The sweeps pack two source channels
+// of the same voxel into a pair, so filter weights (stored channel-minor) load as ready pairs
+// and only the window value has to be duplicated.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 p, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ void fma2(f32x2& acc, f32x2 a, f32x2 b) {
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(a), "l"(b));
+}
+// lane `hi` (0 or 1, a compile-time value after unrolling) of a pair
+__device__ __forceinline__ float lane_of(f32x2 p, int hi) {
+    float lo, up;
+    unpack2(p, lo, up);
+    return hi ? up : lo;
+}
+
+// One filter row (KW taps) of an adjoint sweep over two single-channel planes at once:
+// an[jp][v] += x[w0 + v + PW - kw] * hA[kw][2jp .. 2jp+1], ad likewise from t.  `xrow`/`trow`
+// are ring rows in the shifted layout, `quad` the strip's first window quad, `w_row` the KW x SCH
+// weights of this (kd, kh), channel-minor.
+template <int KW, int NQA>
+__device__ __forceinline__ void adjoint_row2(const float* xrow, const float* trow, int quad,
+                                             const float* w_row, f32x2 (&an)[SCH / 2][VA],
+                                             f32x2 (&ad)[SCH / 2][VA]) {
+    constexpr int PW = KW / 2;
+    float xv[4 * NQA], tv[4 * NQA];
+    load_window<NQA, false>(xrow, quad, xv);
+    load_window<NQA, false>(trow, quad, tv);
+    f32x2 x2[VA + KW - 1], t2[VA + KW - 1];
+#pragma unroll
+    for (int i = 0; i < VA + KW - 1; ++i) {
+        x2[i] = pack2(xv[i], xv[i]);
+        t2[i] = pack2(tv[i], tv[i]);
+    }
+#pragma unroll
+    for (int kw = 0; kw < KW; ++kw) {
+        const float4 w4 = *reinterpret_cast<const float4*>(w_row + kw * SCH);
+        const f32x2 wp[SCH / 2] = {pack2(w4.x, w4.y), pack2(w4.z, w4.w)};
+#pragma unroll
+        for (int jp = 0; jp < SCH / 2; ++jp)
+#pragma unroll
+            for (int v = 0; v < VA; ++v) {
+                fma2(an[jp][v], x2[v + 2 * PW - kw], wp[jp]);
+                fma2(ad[jp][v], t2[v + 2 * PW - kw], wp[jp]);
+            }
+    }
+}
+
 // x / (y) with one reciprocal approximation: |relative error| <= 2 ulp, y > 0 and normal.
 __device__ __forceinline__ float fast_div(float x, float y) { return __fdividef(x, y); }
 

@@ -356,11 +356,15 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
 #pragma unroll
             for (int j = 0; j < SCH; ++j)
                 zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + (long long)d * HW + (long long)hrow * W, w0, W);
-            float an[SCH][VA], ad[SCH][VA];
+            // accumulators hold channel pairs (2jp, 2jp+1) of one voxel
+            f32x2 an[SCH / 2][VA], ad[SCH / 2][VA];
+            {
+                const f32x2 e2 = pack2(P.eps, P.eps);
 #pragma unroll
-            for (int j = 0; j < SCH; ++j)
+                for (int jp = 0; jp < SCH / 2; ++jp)
 #pragma unroll
-                for (int v = 0; v < VA; ++v) { an[j][v] = P.eps; ad[j][v] = P.eps; }
+                    for (int v = 0; v < VA; ++v) { an[jp][v] = e2; ad[jp][v] = e2; }
+            }
 #pragma unroll 1
             for (int kd = 0; kd < KD; ++kd) {
                 const int q = d + PD - kd;
@@ -369,22 +373,9 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
 #pragma unroll
                 for (int kh = 0; kh < KH; ++kh) {
                     const int rr = a_row + PH + PH - kh;  // ring row of h + PH - kh
-                    float xv[4 * NQA], tv[4 * NQA];
-                    load_window<NQA, false>(xring + slot * lay.plane_t + rr * pitch, a_q + 1, xv);
-                    load_window<NQA, false>(t1ring + slot * lay.plane_t + rr * pitch, a_q + 1, tv);
-#pragma unroll
-                    for (int kw = 0; kw < KW; ++kw) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(
-                            wA + ((kd * KH + kh) * KW + kw) * SCH);
-                        const float wj[SCH] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-                        for (int j = 0; j < SCH; ++j)
-#pragma unroll
-                            for (int v = 0; v < VA; ++v) {
-                                an[j][v] = fmaf(xv[v + 2 * PW - kw], wj[j], an[j][v]);
-                                ad[j][v] = fmaf(tv[v + 2 * PW - kw], wj[j], ad[j][v]);
-                            }
-                    }
+                    adjoint_row2<KW, NQA>(xring + slot * lay.plane_t + rr * pitch,
+                                          t1ring + slot * lay.plane_t + rr * pitch, a_q + 1,
+                                          wA + (kd * KH + kh) * KW * SCH, an, ad);
                 }
             }
 #pragma unroll
@@ -395,7 +386,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
                 for (int v = 0; v < VA; ++v) {
                     float s = zj[v] + bj[j];
                     if (P.relu) s = fmaxf(s, 0.0f);
-                    ov[v] = fast_div(s * an[j][v], ad[j][v]);
+                    ov[v] = fast_div(s * lane_of(an[j / 2][v], j & 1), lane_of(ad[j / 2][v], j & 1));
                 }
                 store_strip_global<T, VEC, VA>(og + j * SP + (long long)d * HW + (long long)hrow * W,
                                                w0, W, ov);
