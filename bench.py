@@ -19,6 +19,7 @@ host cores instead.
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -396,14 +397,17 @@ def run_profile_case(args):
     C, r, ks, S = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"], WORKLOAD["spatial"]
     if args.channels:
         C = args.channels
+    if args.ksize:
+        ks = tuple(int(v) for v in args.ksize.split(","))
+        S = S[:len(ks)]
     if args.size:
-        S = (args.size,) * 3
+        S = (args.size,) * len(ks)
     B = args.batch
     dt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
     gen = torch.Generator(device=dev).manual_seed(0)
     x = torch.rand(B, C, *S, device=dev, generator=gen).to(dt).requires_grad_(True)
     z = (torch.randn(B, C * r, *S, device=dev, generator=gen) * 0.5 + 0.3).to(dt).requires_grad_(True)
-    h = (torch.randn(C, r, *ks, device=dev, generator=gen).abs() / 27).requires_grad_(True)
+    h = (torch.randn(C, r, *ks, device=dev, generator=gen).abs() / math.prod(ks)).requires_grad_(True)
     b = (torch.randn(C * r, device=dev, generator=gen) * 0.1).requires_grad_(True)
     g = torch.randn(B, C * r, *S, device=dev, generator=gen).to(dt)
     from deconver_b200 import functional as Fn
@@ -432,7 +436,8 @@ def main():
     ap.add_argument("--batch", type=int, default=1, help="batch of --profile-case")
     ap.add_argument("--dtype", choices=["f32", "bf16"], default="f32", help="dtype of --profile-case")
     ap.add_argument("--channels", type=int, default=0, help="channels of --profile-case (default 64)")
-    ap.add_argument("--size", type=int, default=0, help="cubic extent of --profile-case (default 64)")
+    ap.add_argument("--size", type=int, default=0, help="extent per axis of --profile-case (default 64)")
+    ap.add_argument("--ksize", default="", help="kernel size of --profile-case, e.g. 5,5 (default 3,3,3)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)

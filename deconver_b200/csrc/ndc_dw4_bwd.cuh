@@ -32,7 +32,7 @@ struct RingSmem {
     static constexpr int PD = KD / 2, PH = KH / 2;
     static constexpr int RING = KD > 1 ? KD + 1 : 1;
     int wA, ring0, desc, total_floats, RT, plane_t;
-    __host__ __device__ RingSmem(const Tiling& t, int ntensors, int nthreads) {
+    __host__ __device__ RingSmem(const Tiling& t, int ntensors, int red_floats) {
         RT = t.TH + 2 * PH;
         plane_t = RT * t.pitch;
         int o = 0;
@@ -40,10 +40,8 @@ struct RingSmem {
         o = (o + 3) / 4 * 4;
         ring0 = o; o += ntensors * RING * plane_t;
         desc = o; o += KD > 1 ? 2 * (RT * t.NQ) : 0;
-        // the end-of-kernel reduction (nthreads > 0) reuses the ring area: nthreads rows of
-        // (taps*4 + 5) floats
-        const int red = nthreads * (KD * KH * KW * SCH + 5);
-        if (o - ring0 < red) o = ring0 + red;
+        // the end-of-kernel reduction reuses the ring area and needs red_floats of it
+        if (o - ring0 < red_floats) o = ring0 + red_floats;
         total_floats = (o + 3) / 4 * 4;
     }
 };
@@ -282,7 +280,7 @@ struct KconvSmem {
 // The KD running sums and their aux strips never move between registers: plane q lives in
 // slot q mod KD, and the step body exists in KD rotated copies.
 template <typename T, int KD, int KH, int KW, int NT, bool VEC, bool WGRAD, int WQ>
-__global__ void __launch_bounds__(NT, 2) kconv_kernel(const KconvParams P) {
+__global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2;
     using L = KconvSmem<KD, KH, KW>;
     constexpr int WKP = L::WKP, NSB = L::NSB, KT = KD * KH * KW;
@@ -568,16 +566,32 @@ struct GzParams {
     int relu;
 };
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD, int WQ>
-__global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
+// Floats of shared memory the end-of-kernel combine of gz_kernel needs: one row of sums (+1 pad)
+// per thread.
+template <int KD, int KH, int KW, int CS>
+__host__ __device__ constexpr int gz_combine_floats(int nthreads) {
+    return nthreads * ((KD * KH * KW + 1) * (SCH / CS) + 1);
+}
+
+// CS = channel split: CS threads share one 4-voxel strip and each takes SCH/CS channels (a
+// whole number of pairs).  The correlation sums are per channel, so CS = 2 halves the registers
+// a thread needs (54 + 2 sums instead of 108 + 4) and twice as many warps fit on an SM; the two
+// threads sit in adjacent lanes and read the same window quads.
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, bool WGRAD, int WQ, int CS>
+__global__ void __launch_bounds__(NT, CS == 2 ? 512 / NT : 256 / NT) gz_kernel(const GzParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
     using L = RingSmem<KD, KH, KW>;
     constexpr int RING = L::RING;
     constexpr int NQA = 1 + (2 * PW + 3) / 4;
-    constexpr int NACC = (WGRAD ? KT * SCH : 0) + SCH;
+    constexpr int CH = SCH / CS;          // channels per thread
+    constexpr int NP = CH / 2;            // channel pairs per thread
+    constexpr int NACC = (WGRAD ? KT * SCH : 0) + SCH;      // sums per CTA record
+    constexpr int NLOC = (WGRAD ? KT * CH : 0) + CH;        // sums per thread
+    static_assert(CS == 1 || CS == 2, "channel split");
     extern __shared__ __align__(16) float smem[];
-    const L lay(P.t, 1, NT);
+    const L lay(P.t, 1, gz_combine_floats<KD, KH, KW, CS>(NT));
     const int tid = threadIdx.x;
+    const int part = tid % CS;            // which channels: part*CH .. part*CH + CH-1
     const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch, H = P.H,
               W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
     const long long HW = (long long)H * W, SP = HW * D;
@@ -593,8 +607,8 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     const int RT = lay.RT;
 
     const float* tg = P.gt1 + (long long)bc * SP;
-    const T* zg = reinterpret_cast<const T*>(P.z) + (long long)bc * SCH * SP;
-    T* gzg = P.gz ? reinterpret_cast<T*>(P.gz) + (long long)bc * SCH * SP : nullptr;
+    const T* zg = reinterpret_cast<const T*>(P.z) + ((long long)bc * SCH + part * CH) * SP;
+    T* gzg = P.gz ? reinterpret_cast<T*>(P.gz) + ((long long)bc * SCH + part * CH) * SP : nullptr;
 
     float* wA = smem + lay.wA;
     float* ring = smem + lay.ring0;
@@ -606,17 +620,17 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     }
     const int nx = RT * NQ;
     if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
-    float bj[SCH];
+    float bj[CH];
 #pragma unroll
-    for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
-    // filter-gradient sums [tap][channel pair] (if WGRAD), and 4 bias sums
-    constexpr int NW2 = (NACC - SCH) / 2 > 0 ? (NACC - SCH) / 2 : 1;
+    for (int j = 0; j < CH; ++j) bj[j] = P.bias ? P.bias[c * SCH + part * CH + j] : 0.0f;
+    // filter-gradient sums [tap][channel pair] (if WGRAD), and the bias sums
+    constexpr int NW2 = WGRAD ? KT * NP : 1;
     f32x2 acc2[NW2];
-    float gbs[SCH];
+    float gbs[CH];
 #pragma unroll
     for (int k = 0; k < NW2; ++k) acc2[k] = pack2(0.0f, 0.0f);
 #pragma unroll
-    for (int j = 0; j < SCH; ++j) gbs[j] = 0.0f;
+    for (int j = 0; j < CH; ++j) gbs[j] = 0.0f;
     __syncthreads();
 
     const int qbase = d0 - PD - 1;
@@ -637,20 +651,22 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
     __syncthreads();
 
     const int items = TH * NQ;
+    constexpr int NSLOT = NT / CS;        // strips in flight per CTA
+    const int slot0 = tid / CS;
     // z (and the direct term) of the next item are fetched while the current one is computed
-    constexpr int NSTR = 2 * SCH;
+    constexpr int NSTR = 2 * CH;
     StripFetcher<T, VEC, NSTR, NT> fetch(smem + lay.total_floats);
     auto strip_ptrs = [&](int d, int item, const T* (&ptr)[NSTR]) {
         const long long off = (long long)d * HW + (long long)(h0 + item / NQ) * W + VA * (item % NQ);
 #pragma unroll
-        for (int j = 0; j < SCH; ++j) {
+        for (int j = 0; j < CH; ++j) {
             ptr[j] = zg + j * SP + off;
-            ptr[SCH + j] = (gzg ? gzg : zg) + j * SP + off;
+            ptr[CH + j] = (gzg ? gzg : zg) + j * SP + off;
         }
     };
-    if (tid < items && d0 < d1) {
+    if (slot0 < items && d0 < d1) {
         const T* ptr[NSTR];
-        strip_ptrs(d0, tid, ptr);
+        strip_ptrs(d0, slot0, ptr);
         fetch.request(ptr);
     }
     for (int d = d0; d < d1; ++d) {
@@ -669,7 +685,7 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
             }
         }
 #pragma unroll 1
-        for (int item = tid; item < items; item += NT) {
+        for (int item = slot0; item < items; item += NSLOT) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
             const long long off = (long long)d * HW + (long long)hrow * W;
@@ -678,16 +694,16 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
                 const T* ptr[NSTR];
                 strip_ptrs(d, item, ptr);
                 fetch.receive(ptr, w0, W, strips);
-                int nd = d, nitem = item + NT;
-                if (nitem >= items) { nitem = tid; nd = d + 1; }
+                int nd = d, nitem = item + NSLOT;
+                if (nitem >= items) { nitem = slot0; nd = d + 1; }
                 if (nd < d1 && nitem < items) {
                     strip_ptrs(nd, nitem, ptr);
                     fetch.request(ptr);
                 }
             }
-            float sv[SCH][VA], pre[SCH][VA];
+            float sv[CH][VA], pre[CH][VA];
 #pragma unroll
-            for (int j = 0; j < SCH; ++j) {
+            for (int j = 0; j < CH; ++j) {
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
                     pre[j][v] = strips[j][v] + bj[j];
@@ -697,12 +713,12 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
             }
             // channel pairs (2jp, 2jp+1) of one voxel share a register pair; the accumulators
             // start from the direct term
-            f32x2 ag[SCH / 2][VA], s2[SCH / 2][VA];
+            f32x2 ag[NP][VA], s2[NP][VA];
 #pragma unroll
-            for (int jp = 0; jp < SCH / 2; ++jp)
+            for (int jp = 0; jp < NP; ++jp)
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
-                    ag[jp][v] = gzg ? pack2(strips[SCH + 2 * jp][v], strips[SCH + 2 * jp + 1][v])
+                    ag[jp][v] = gzg ? pack2(strips[CH + 2 * jp][v], strips[CH + 2 * jp + 1][v])
                                     : pack2(0.0f, 0.0f);
                     s2[jp][v] = pack2(sv[2 * jp][v], sv[2 * jp + 1][v]);
                 }
@@ -721,12 +737,19 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
                     for (int i = 0; i < VA + KW - 1; ++i) t2[i] = pack2(tv[i], tv[i]);
 #pragma unroll
                     for (int kw = 0; kw < KW; ++kw) {
-                        const float4 w4 = *reinterpret_cast<const float4*>(
-                            wA + ((kd * KH + kh) * KW + kw) * SCH);
-                        const f32x2 wp[SCH / 2] = {pack2(w4.x, w4.y), pack2(w4.z, w4.w)};
+                        const float* wp4 = wA + ((kd * KH + kh) * KW + kw) * SCH + part * CH;
+                        f32x2 wp[NP];
+                        if (CS == 1) {
+                            const float4 w4 = *reinterpret_cast<const float4*>(wp4);
+                            wp[0] = pack2(w4.x, w4.y);
+                            wp[NP - 1] = pack2(w4.z, w4.w);
+                        } else {
+                            const float2 w2 = *reinterpret_cast<const float2*>(wp4);
+                            wp[0] = pack2(w2.x, w2.y);
+                        }
 #pragma unroll
-                        for (int jp = 0; jp < SCH / 2; ++jp) {
-                            const int k2 = WGRAD ? ((kd * KH + kh) * KW + kw) * (SCH / 2) + jp : 0;
+                        for (int jp = 0; jp < NP; ++jp) {
+                            const int k2 = WGRAD ? ((kd * KH + kh) * KW + kw) * NP + jp : 0;
                             f32x2 a = acc2[k2];
 #pragma unroll
                             for (int v = 0; v < VA; ++v) {
@@ -740,7 +763,7 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
             }
             if (gzg) {
 #pragma unroll
-                for (int j = 0; j < SCH; ++j) {
+                for (int j = 0; j < CH; ++j) {
                     float dv[VA];
 #pragma unroll
                     for (int v = 0; v < VA; ++v) {
@@ -768,19 +791,23 @@ __global__ void __launch_bounds__(NT, 2) gz_kernel(const GzParams P) {
         __syncthreads();
     }
     float* out = P.partial + (long long)blockIdx.x * kPartialStride;
-    // record layout: [0, taps*4) filter sums (zero if not WGRAD), [124, 128) bias sums
-    constexpr int LD = NACC + 1;
+    // Per-CTA combine in a fixed order.  Thread rows hold [tap][own channel] filter sums, then
+    // the own bias sums; record layout: [0, taps*4) filter sums [tap][channel] (zero if not
+    // WGRAD), [124, 128) bias sums.
+    constexpr int LD = NLOC + 1;
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < NACC - SCH; ++k) ring[tid * LD + k] = lane_of(acc2[k / 2], k & 1);
+    for (int k = 0; k < NLOC - CH; ++k) ring[tid * LD + k] = lane_of(acc2[k / 2], k & 1);
 #pragma unroll
-    for (int j = 0; j < SCH; ++j) ring[tid * LD + NACC - SCH + j] = gbs[j];
+    for (int j = 0; j < CH; ++j) ring[tid * LD + NLOC - CH + j] = gbs[j];
     __syncthreads();
     for (int k = tid; k < NACC; k += NT) {
-        float s = 0.0f;
-        for (int i = 0; i < NT; ++i) s += ring[i * LD + k];
         const bool is_bias = k >= NACC - SCH;
-        out[is_bias ? kPartialStride - SCH + (k - (NACC - SCH)) : k] = s;
+        const int j = is_bias ? k - (NACC - SCH) : k % SCH;          // channel of this sum
+        const int loc = is_bias ? NLOC - CH + j % CH : (k / SCH) * CH + j % CH;
+        float s = 0.0f;
+        for (int i = j / CH; i < NT; i += CS) s += ring[i * LD + loc];
+        out[is_bias ? kPartialStride - SCH + j : k] = s;
     }
 }
 

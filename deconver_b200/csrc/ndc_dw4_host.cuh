@@ -18,29 +18,38 @@ template <int KD, int KH, int KW> struct FwdShape;
 template <> struct FwdShape<3, 3, 3> { static constexpr int NT = 256, MAXZ = 5, MAXX = 1, MINB = 2; };
 template <> struct FwdShape<1, 5, 5> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
 template <> struct FwdShape<1, 3, 3> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
+// 2-D images of 65..256 columns run as volumes of one-row planes: rows become the marching axis,
+// so nothing is recomputed between row bands and the loads of the next row overlap the work
+// on this one.  A CTA is as wide as one row has 4-voxel strips.
+template <int NT_> struct FwdRows { static constexpr int NT = NT_, MAXZ = 4, MAXX = 1, MINB = 384 / NT_; };
 
 inline bool shape_supported(int kD, int kH, int kW) {
     return (kD == 3 && kH == 3 && kW == 3) || (kD == 1 && kH == 5 && kW == 5) ||
            (kD == 1 && kH == 3 && kW == 3);
 }
 
-// Chunks along depth: enough CTAs for about `waves` rounds of two CTAs per SM, but chunks of
-// at least 16 planes (every chunk recomputes 2*PD planes of its neighbours).
-inline void plan_depth(int KD, int D, long long ctas_per_chunk, int waves, Tiling& t) {
+// Chunks along depth: enough CTAs for about `waves` rounds of `ctas_per_sm` CTAs per SM, but
+// chunks of at least 16*PD planes (every chunk recomputes 2*PD planes of its neighbours); only
+// a grid that would not even fill the GPU once is cut finer, down to 4*PD planes.
+inline void plan_depth(int KD, int D, long long ctas_per_chunk, int waves, Tiling& t,
+                       int ctas_per_sm = 2) {
     if (KD == 1) {
         t.DC = 1;
     } else {
-        const long long target = (long long)waves * 2 * kNumSMs;
-        long long ndc = target / std::max(1LL, ctas_per_chunk);
-        ndc = std::max(1LL, std::min(ndc, (long long)std::max(1, D / 16)));
+        const int PD = KD / 2;
+        const long long per = std::max(1LL, ctas_per_chunk);
+        const long long one_wave = (long long)ctas_per_sm * kNumSMs;
+        long long ndc = std::min(waves * one_wave / per, (long long)std::max(1, D / (16 * PD)));
+        if (ndc * per < one_wave)
+            ndc = std::min((one_wave + per - 1) / per, (long long)std::max(1, D / (4 * PD)));
+        ndc = std::max(1LL, ndc);
         t.DC = (int)((D + ndc - 1) / ndc);
     }
     t.ndc = (D + t.DC - 1) / t.DC;
 }
 
-template <int KD, int KH, int KW>
+template <int KD, int KH, int KW, typename S = FwdShape<KD, KH, KW>>
 inline bool plan_fwd(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
-    using S = FwdShape<KD, KH, KW>;
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29)) return false;  // 32-bit offsets inside a slab
     if (W > 256) return false;
@@ -61,7 +70,7 @@ inline bool plan_fwd(int D, int H, int W, long long BC, Tiling& t, size_t& smem_
     if (TH < 1 || bytes(TH) > kSmemMax || SCH * (TH + 4 * PH) * t.pitch > 65535) return false;
     t.nth = (H + TH - 1) / TH;
     t.TH = (H + t.nth - 1) / t.nth;
-    plan_depth(KD, D, BC * t.nth, 5, t);
+    plan_depth(KD, D, BC * t.nth, 5, t, S::MINB);
     smem_bytes = bytes(t.TH);
     return true;
 }
@@ -70,9 +79,8 @@ inline bool aligned_for_vec(const void* p, int dtype) {
     return ((uintptr_t)p % (dtype == NDC_BF16 ? 8 : 16)) == 0;
 }
 
-template <typename T, int KD, int KH, int KW, bool VEC, int WQ>
+template <typename T, int KD, int KH, int KW, typename S, bool VEC, int WQ>
 cudaError_t launch_fwd(const FwdParams& P, size_t smem_bytes, long long BC, cudaStream_t st) {
-    using S = FwdShape<KD, KH, KW>;
     auto kern = fwd_kernel<T, KD, KH, KW, S::NT, S::MAXZ, S::MAXX, S::MINB, VEC, WQ>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem_bytes);
@@ -84,13 +92,13 @@ cudaError_t launch_fwd(const FwdParams& P, size_t smem_bytes, long long BC, cuda
     return cudaGetLastError();
 }
 
-template <typename T, int KD, int KH, int KW>
+template <typename T, int KD, int KH, int KW, typename S = FwdShape<KD, KH, KW>>
 cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, const float* bias,
                           T* out, T* t1, int dtype, cudaStream_t st, bool& handled) {
     FwdParams P;
     size_t smem = 0;
     const long long BC = (long long)g.B * g.G;
-    handled = plan_fwd<KD, KH, KW>(g.D, g.H, g.W, BC, P.t, smem);
+    handled = plan_fwd<KD, KH, KW, S>(g.D, g.H, g.W, BC, P.t, smem);
     if (!handled) return cudaSuccess;
     P.x = x; P.z = z; P.h = h; P.bias = bias; P.out = out; P.t1 = t1;
     P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W;
@@ -98,27 +106,35 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
     const bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
                      aligned_for_vec(out, dtype) && aligned_for_vec(t1, dtype);
     // widths that occur in the published configurations get kernels with a compile-time width
-    if constexpr (KD > 1) {
-        if (vec && g.W == 64) return launch_fwd<T, KD, KH, KW, true, 16>(P, smem, BC, st);
-        if (vec && g.W == 128) return launch_fwd<T, KD, KH, KW, true, 32>(P, smem, BC, st);
+    if constexpr (KD > 1 && KH > 1) {
+        if (vec && g.W == 64) return launch_fwd<T, KD, KH, KW, S, true, 16>(P, smem, BC, st);
+        if (vec && g.W == 128) return launch_fwd<T, KD, KH, KW, S, true, 32>(P, smem, BC, st);
     }
-    return vec ? launch_fwd<T, KD, KH, KW, true, 0>(P, smem, BC, st)
-               : launch_fwd<T, KD, KH, KW, false, 0>(P, smem, BC, st);
+    if constexpr (KD > 1 && KH == 1) {
+        if (vec && g.W == 4 * S::NT) return launch_fwd<T, KD, KH, KW, S, true, S::NT>(P, smem, BC, st);
+    }
+    return vec ? launch_fwd<T, KD, KH, KW, S, true, 0>(P, smem, BC, st)
+               : launch_fwd<T, KD, KH, KW, S, false, 0>(P, smem, BC, st);
 }
 
 // ---------------------------------------------------------------------------- backward
 
-constexpr int kRatioNT = 128;   // ratio_kernel threads
-constexpr int kRatioMAXX = 2;   // its prefetch registers (quads) per tensor
-constexpr int kRingNT = 128;    // gz_kernel threads
-constexpr int kRingMAXX = 4;
-constexpr int kKconvNT = 192;   // 48 strip slots x 4 channel lanes
+// Threads (and prefetch registers, in quads per thread) of the three backward kernels.
+// Bands: a CTA owns a band of rows of every plane.  kconv: 48 strip slots x 4 channel lanes.
+struct BwdBands {
+    static constexpr int RatioNT = 128, RatioMAXX = 2, KconvNT = 192, GzNT = 128, GzMAXX = 4;
+};
+// Rows: one-row planes of NQ 4-voxel strips (2-D images run as volumes, see FwdRows).
+template <int NQ_> struct BwdRows {
+    static constexpr int RatioNT = NQ_, RatioMAXX = 1, KconvNT = 2 * NQ_, GzNT = NQ_, GzMAXX = 1;
+};
+constexpr int kGzCS = 1;        // channel split of gz_kernel (2 was measured no faster)
 
 // Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
 template <int KD, int KH, int KW>
 inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, int maxx,
-                      int red_threads, size_t extra_bytes, size_t smem_target, Tiling& t,
-                      size_t& smem_bytes) {
+                      int red_floats, size_t extra_bytes, size_t smem_target, int ctas_per_sm,
+                      Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
     t.NQ = (W + 3) / 4;
@@ -127,19 +143,19 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
     if (KD > 1) TH = std::min(TH, nt * maxx / t.NQ - 2 * PH);
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
-        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, red_threads).total_floats * sizeof(float) +
+        return (size_t)RingSmem<KD, KH, KW>(q, ntensors, red_floats).total_floats * sizeof(float) +
                extra_bytes;
     };
     while (TH > 1 && (bytes(TH) > smem_target || (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
     t.nth = (H + TH - 1) / TH;
     t.TH = (H + t.nth - 1) / t.nth;
-    plan_depth(KD, D, BC * t.nth, 6, t);
+    plan_depth(KD, D, BC * t.nth, 6, t, ctas_per_sm);
     smem_bytes = bytes(t.TH);
     return true;
 }
 
-template <int KD, int KH, int KW>
+template <int KD, int KH, int KW, int NT>
 inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
@@ -148,17 +164,17 @@ inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& sme
     const int NS8 = (t.NQ + 1) / 2;
     int TH = H;
     if (KD > 1) {
-        TH = std::min(TH, (kKconvNT / SCH) / NS8);
+        TH = std::min(TH, (NT / SCH) / NS8);
     }
     auto bytes = [&](int th) {
         Tiling q = t; q.TH = th;
-        return (size_t)KconvSmem<KD, KH, KW>(q, kKconvNT).total_floats * sizeof(float);
+        return (size_t)KconvSmem<KD, KH, KW>(q, NT).total_floats * sizeof(float);
     };
     while (TH > 1 && (bytes(TH) > 72 * 1024 || SCH * (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
     t.nth = (H + TH - 1) / TH;
     t.TH = (H + t.nth - 1) / t.nth;
-    plan_depth(KD, D, 2 * BC * t.nth, 6, t);
+    plan_depth(KD, D, 2 * BC * t.nth, 6, t, 384 / NT);
     smem_bytes = bytes(t.TH);
     return true;
 }
@@ -168,17 +184,21 @@ struct BwdPlan {
     size_t smem_ratio, smem_kconv, smem_gz;
     size_t off_gnum, off_gden, off_gt1, off_gxtmp, off_pa, off_pa2, off_pb, bytes;
     long long n_ratio, n_kconv, n_gz;   // CTAs (kconv: per tensor; = partial records)
+    int rows;                           // 0: band kernels; else the rows class planned
 };
 
-template <int KD, int KH, int KW>
+template <int KD, int KH, int KW, typename S>
 inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     const long long BC = (long long)g.B * g.G;
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, kRatioNT, kRatioMAXX, 0, 0, 56 * 1024, p.ratio, p.smem_ratio))
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, S::RatioNT, S::RatioMAXX, 0, 0, 56 * 1024,
+                               512 / S::RatioNT, p.ratio, p.smem_ratio))
         return false;
-    if (!plan_kconv<KD, KH, KW>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
-    // gz_kernel also stages two sets of 8 strips per thread (z and the direct term)
-    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, kRingNT, kRingMAXX, kRingNT,
-                               (size_t)2 * 2 * SCH * kRingNT * 16, kSmemTwoPerSM, p.gz, p.smem_gz))
+    if (!plan_kconv<KD, KH, KW, S::KconvNT>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
+    // gz_kernel also double-buffers its strips of z and of the direct term (16 bytes each)
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, S::GzNT, S::GzMAXX,
+                               gz_combine_floats<KD, KH, KW, kGzCS>(S::GzNT),
+                               (size_t)2 * 2 * (SCH / kGzCS) * S::GzNT * 16, kSmemTwoPerSM,
+                               256 / S::GzNT, p.gz, p.smem_gz))
         return false;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     const size_t src = (size_t)BC * SCH * g.SP * sizeof(float);
@@ -198,11 +218,33 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     return true;
 }
 
+// 2-D images of 65..256 columns are run as volumes of one-row planes (the same memory and the
+// same filter layout): returns the strips per row the kernels are built for, 0 for other shapes.
+inline int rows_class(const Geo& g) {
+    if (g.kD != 1 || g.kH != 5 || g.kW != 5 || g.H < 32) return 0;
+    if (g.W > 128 && g.W <= 256) return 64;
+    if (g.W > 64 && g.W <= 128) return 32;
+    return 0;
+}
+inline Geo as_rows(const Geo& g) {
+    Geo v = g;
+    v.D = g.H; v.H = 1; v.kD = g.kH; v.kH = 1; v.pD = g.pH; v.pH = 0;
+    return v;
+}
+
 inline bool plan_bwd_any(const Geo& g, BwdPlan& p) {
+    p.rows = 0;
     if (g.m != 1 || g.sc != SCH) return false;
-    if (g.kD == 3 && g.kH == 3 && g.kW == 3) return plan_bwd<3, 3, 3>(g, p);
-    if (g.kD == 1 && g.kH == 5 && g.kW == 5) return plan_bwd<1, 5, 5>(g, p);
-    if (g.kD == 1 && g.kH == 3 && g.kW == 3) return plan_bwd<1, 3, 3>(g, p);
+    if (g.kD == 3 && g.kH == 3 && g.kW == 3) return plan_bwd<3, 3, 3, BwdBands>(g, p);
+    if (g.kD == 1 && g.kH == 5 && g.kW == 5) {
+        const int rc = rows_class(g);
+        p.rows = rc;
+        if (rc == 64 && plan_bwd<5, 1, 5, BwdRows<64>>(as_rows(g), p)) return true;
+        if (rc == 32 && plan_bwd<5, 1, 5, BwdRows<32>>(as_rows(g), p)) return true;
+        p.rows = 0;
+        return plan_bwd<1, 5, 5, BwdBands>(g, p);
+    }
+    if (g.kD == 1 && g.kH == 3 && g.kW == 3) return plan_bwd<1, 3, 3, BwdBands>(g, p);
     return false;
 }
 
@@ -217,7 +259,7 @@ inline cudaError_t set_smem(K kern, size_t bytes) {
         if (_e != cudaSuccess) return _e;       \
     } while (0)
 
-template <typename T, int KD, int KH, int KW, bool VEC, int WQ>
+template <typename T, int KD, int KH, int KW, typename S, bool VEC, int WQ>
 cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                             const float* h, const float* bias, const T* gout, T* gx, T* gz,
                             float* gh, float* gb, void* ws, cudaStream_t st) {
@@ -232,9 +274,9 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;
         P.gnum = gnum; P.gden = gden; P.gz = gz;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.ratio; P.eps = g.eps; P.relu = g.relu;
-        auto kern = ratio_kernel<T, KD, KH, KW, kRatioNT, kRatioMAXX, VEC, WQ>;
+        auto kern = ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, VEC, WQ>;
         NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
-        kern<<<(unsigned)p.n_ratio, kRatioNT, p.smem_ratio, st>>>(P);
+        kern<<<(unsigned)p.n_ratio, S::RatioNT, p.smem_ratio, st>>>(P);
         launched();
     }
     {
@@ -258,13 +300,13 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         if (n > 0) {
             dim3 grid((unsigned)p.n_kconv, n);
             if (gh) {
-                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, true, WQ>;
+                auto kern = kconv_kernel<T, KD, KH, KW, S::KconvNT, VEC, true, WQ>;
                 NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
-                kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
+                kern<<<grid, S::KconvNT, p.smem_kconv, st>>>(P);
             } else {
-                auto kern = kconv_kernel<T, KD, KH, KW, kKconvNT, VEC, false, WQ>;
+                auto kern = kconv_kernel<T, KD, KH, KW, S::KconvNT, VEC, false, WQ>;
                 NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
-                kern<<<grid, kKconvNT, p.smem_kconv, st>>>(P);
+                kern<<<grid, S::KconvNT, p.smem_kconv, st>>>(P);
             }
             launched();
         }
@@ -274,13 +316,13 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.gt1 = gt1; P.z = z; P.gz = gz; P.h = h; P.bias = bias; P.partial = pb;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.gz; P.relu = g.relu;
         if (gh) {
-            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, true, WQ>;
+            auto kern = gz_kernel<T, KD, KH, KW, S::GzNT, S::GzMAXX, VEC, true, WQ, kGzCS>;
             NDC_CUDA_TRY(set_smem(kern, p.smem_gz));
-            kern<<<(unsigned)p.n_gz, kRingNT, p.smem_gz, st>>>(P);
+            kern<<<(unsigned)p.n_gz, S::GzNT, p.smem_gz, st>>>(P);
         } else {
-            auto kern = gz_kernel<T, KD, KH, KW, kRingNT, kRingMAXX, VEC, false, WQ>;
+            auto kern = gz_kernel<T, KD, KH, KW, S::GzNT, S::GzMAXX, VEC, false, WQ, kGzCS>;
             NDC_CUDA_TRY(set_smem(kern, p.smem_gz));
-            kern<<<(unsigned)p.n_gz, kRingNT, p.smem_gz, st>>>(P);
+            kern<<<(unsigned)p.n_gz, S::GzNT, p.smem_gz, st>>>(P);
         }
         launched();
     }
@@ -299,7 +341,7 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
     return cudaGetLastError();
 }
 
-template <typename T, int KD, int KH, int KW>
+template <typename T, int KD, int KH, int KW, typename S>
 cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                            const float* h, const float* bias, const T* gout, T* gx, T* gz,
                            float* gh, float* gb, void* ws, int dtype, cudaStream_t st) {
@@ -307,25 +349,36 @@ cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* 
                aligned_for_vec(t1, dtype) && aligned_for_vec(gout, dtype);
     if (gx) vec = vec && aligned_for_vec(gx, dtype);
     if (gz) vec = vec && aligned_for_vec(gz, dtype);
-    if constexpr (KD > 1) {
+    // widths that occur in the published configurations get kernels with a compile-time width
+    if constexpr (KD > 1 && KH > 1) {
         if (vec && g.W == 64)
-            return backward_launch<T, KD, KH, KW, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+            return backward_launch<T, KD, KH, KW, S, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
         if (vec && g.W == 128)
-            return backward_launch<T, KD, KH, KW, true, 32>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+            return backward_launch<T, KD, KH, KW, S, true, 32>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
     }
-    return vec ? backward_launch<T, KD, KH, KW, true, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
-               : backward_launch<T, KD, KH, KW, false, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+    if constexpr (KD > 1 && KH == 1) {
+        if (vec && g.W == 4 * S::RatioNT)
+            return backward_launch<T, KD, KH, KW, S, true, S::RatioNT>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+    }
+    return vec ? backward_launch<T, KD, KH, KW, S, true, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
+               : backward_launch<T, KD, KH, KW, S, false, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
 }
 
+// `p` must come from plan_bwd_any(g): the same rule picks the kernel family here.
 template <typename T>
 cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                      const float* h, const float* bias, const T* gout, T* gx, T* gz, float* gh,
                      float* gb, void* ws, int dtype, cudaStream_t st) {
     if (g.kD == 3)
-        return backward_shape<T, 3, 3, 3>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
-    if (g.kH == 5)
-        return backward_shape<T, 1, 5, 5>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
-    return backward_shape<T, 1, 3, 3>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+        return backward_shape<T, 3, 3, 3, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    if (g.kH == 5) {
+        if (p.rows == 64)
+            return backward_shape<T, 5, 1, 5, BwdRows<64>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+        if (p.rows == 32)
+            return backward_shape<T, 5, 1, 5, BwdRows<32>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+        return backward_shape<T, 1, 5, 5, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    }
+    return backward_shape<T, 1, 3, 3, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
 }
 
 // Whether the tiled kernels take this geometry (pointer alignment only affects vector width).
@@ -347,8 +400,17 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
     if (g.m != 1 || g.sc != SCH) return cudaSuccess;
     if (g.kD == 3 && g.kH == 3 && g.kW == 3)
         return forward_shape<T, 3, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
-    if (g.kD == 1 && g.kH == 5 && g.kW == 5)
+    if (g.kD == 1 && g.kH == 5 && g.kW == 5) {
+        const int rc = rows_class(g);
+        if (rc) {
+            const Geo v = as_rows(g);
+            cudaError_t e = rc == 64
+                ? forward_shape<T, 5, 1, 5, FwdRows<64>>(v, x, z, h, bias, out, t1, dtype, st, handled)
+                : forward_shape<T, 5, 1, 5, FwdRows<32>>(v, x, z, h, bias, out, t1, dtype, st, handled);
+            if (handled || e != cudaSuccess) return e;
+        }
         return forward_shape<T, 1, 5, 5>(g, x, z, h, bias, out, t1, dtype, st, handled);
+    }
     if (g.kD == 1 && g.kH == 3 && g.kW == 3)
         return forward_shape<T, 1, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
     return cudaSuccess;
