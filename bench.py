@@ -40,9 +40,9 @@ WORKLOAD_NAME = ("single 3D NDC mixer layer fwd+bwd (dX, dK), fp32, X (2,64,64,6
 # measured on this pool's B200 with an FFMA-only kernel (profiles/fp32_fma_peak.md)
 FP32_FMA_PEAK_TFLOPS = 72.6
 # DRAM bytes (read + write) per ndc_bwd call: ncu capture at batch 1
-# (profiles/ndc_kernels_cfg3_b1_ncu_full.md: ratio 1443 MB + kconv 833 MB + gz 842 MB),
+# (profiles/ndc_kernels_cfg3_b1_ncu_full.md: ratio 1445 MB + kconv 830 MB + gz 842 MB),
 # scaled by 2 to the bench workload's batch of 2 (traffic is proportional to voxels)
-BWD_DRAM_TRAFFIC_BYTES = 2 * (1443 + 833 + 842) * 1000 * 1000
+BWD_DRAM_TRAFFIC_BYTES = 2 * (1445 + 830 + 842) * 1000 * 1000
 
 
 def load_peaks():
