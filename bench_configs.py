@@ -199,16 +199,43 @@ def config_4(dc, args):
     opt = torch.optim.SGD(params, lr=1e-2, momentum=0.0)
     clock = LayerClock(model, cls)
 
-    def step():
-        for p in params:
-            p.grad = None
+    def fwd_bwd():
         out = model(x)
         # mean over the local shard; equal shards, so the rank average is the global-batch mean
         loss = torch.nn.functional.binary_cross_entropy_with_logits(out.float(), y.float())
         loss.backward()
+        return loss
+
+    def eager_step():
+        for p in params:
+            p.grad = None
+        loss = fwd_bwd()
         bucket.allreduce_mean()
         opt.step()
         return loss
+
+    step = eager_step
+    if args.graph:
+        # forward + backward + gradient gather replayed as one CUDA graph (x, y and the
+        # gradients keep their addresses); the all-reduce and the optimizer stay outside
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                eager_step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for p in params:
+            p.grad = None
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_loss = fwd_bwd()
+            bucket.gather()
+        def step():
+            graph.replay()
+            bucket.allreduce_mean(gather=False)
+            opt.step()
+            return static_loss
 
     for _ in range(3):
         step()
@@ -230,7 +257,7 @@ def config_4(dc, args):
         model(x)
     ndc_fwd = clock.total_ms()
     emit(config=4, n_gpus=world, global_batch=16, per_gpu_batch=nb, dtype="bfloat16",
-         ms_per_step=ms, voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss),
+         cuda_graph=bool(args.graph), ms_per_step=ms, voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss),
          ndc_forward_ms_per_rank=ndc_fwd, params=sum(p.numel() for p in params))
     if dist.is_initialized():
         dist.destroy_process_group()
@@ -279,6 +306,8 @@ def main():
     ap.add_argument("--config", required=True, choices=["triton", "2", "4", "5"])
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--chunk", type=int, default=4)
+    ap.add_argument("--graph", action="store_true",
+                    help="config 4: replay forward+backward as one CUDA graph")
     ap.add_argument("--per-gpu-batch", type=int, default=0,
                     help="config 4: override the per-GPU batch (single-GPU experiments)")
     args = ap.parse_args()

@@ -221,7 +221,7 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
 // 2-D images of 65..256 columns are run as volumes of one-row planes (the same memory and the
 // same filter layout): returns the strips per row the kernels are built for, 0 for other shapes.
 inline int rows_class(const Geo& g) {
-    if (g.kD != 1 || g.kH != 5 || g.kW != 5 || g.H < 32) return 0;
+    if (g.D != 1 || g.kD != 1 || g.kH != 5 || g.kW != 5 || g.H < 32) return 0;
     if (g.W > 128 && g.W <= 256) return 64;
     if (g.W > 64 && g.W <= 128) return 32;
     return 0;

@@ -82,22 +82,33 @@ class GradBucket:
         self.attach()
 
     def gather(self) -> None:
-        """Bring gradients that autograd placed elsewhere (or in another dtype) into the bucket."""
+        """Bring gradients that autograd placed elsewhere (or in another dtype) into the bucket:
+        one multi-tensor copy, not one launch per parameter."""
+        src, dst = [], []
         for p, v in zip(self.params, self._views):
             if p.grad is None:
                 v.zero_()
             elif p.grad.data_ptr() != v.data_ptr():
-                v.copy_(p.grad)
+                src.append(p.grad)
+                dst.append(v)
+        if dst:
+            torch._foreach_copy_(dst, src)
 
     def scatter(self) -> None:
         """Write reduced values back to gradients that are not views of the bucket."""
+        src, dst = [], []
         for p, v in zip(self.params, self._views):
             if p.grad is not None and p.grad.data_ptr() != v.data_ptr():
-                p.grad.copy_(v)
+                src.append(v)
+                dst.append(p.grad)
+        if dst:
+            torch._foreach_copy_(dst, src)
 
-    def allreduce_mean(self, async_op: bool = False):
-        """Average the bucket over the group (sum, then scale by 1/world)."""
-        self.gather()
+    def allreduce_mean(self, async_op: bool = False, gather: bool = True):
+        """Average the bucket over the group (sum, then scale by 1/world).  `gather=False` when
+        the caller has already gathered (e.g. inside a captured graph)."""
+        if gather:
+            self.gather()
         if not dist.is_initialized() or dist.get_world_size(self.group) == 1:
             return None
         world = dist.get_world_size(self.group)

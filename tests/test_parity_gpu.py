@@ -337,7 +337,9 @@ def test_tiled_kernels_match_generic_kernels_on_random_geometries(dev):
               # fewer rows than one chunk, chunk tails, the narrowest and the shortest image taken
               (1, 2, (5, 5), (33, 67), True), (2, 1, (5, 5), (100, 129), True),
               (1, 1, (5, 5), (45, 255), False), (1, 1, (5, 5), (300, 128), True),
-              (1, 3, (5, 5), (32, 65), True), (1, 1, (5, 5), (31, 200), True)]
+              (1, 3, (5, 5), (32, 65), True), (1, 1, (5, 5), (31, 200), True),
+              # a volume with a flat 1x5x5 kernel is not an image: stays on the band kernels
+              (1, 2, (1, 5, 5), (3, 40, 100), True)]
     for B, C, ks, spatial, relu in cases:
         gen = torch.Generator(device=dev).manual_seed(B * 1000 + C * 100 + sum(spatial))
         x = torch.rand(B, C, *spatial, device=dev, generator=gen)
