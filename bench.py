@@ -374,7 +374,7 @@ def run_b200(args):
             "workload": WORKLOAD_NAME, "per_gpu_batch": B, "global_batch": B * world,
             "parallelism": f"batch-sharded x{world}" + (", NCCL grad all-reduce" if world > 1 else ""),
             "l2": "inputs larger than L2 (x 134 MB, z/out/gout 537 MB each vs 126 MB L2)",
-            "kernel_path": {0: "generic", 1: "depthwise4"}.get(pth.value, "?"),
+            "kernel_path": {0: "generic", 1: "depthwise4", 2: "depthwise4_rows"}.get(pth.value, "?"),
         },
         "roofline": roofline,
         "clocks": clocks.summary(),

@@ -11,7 +11,7 @@ from ._build import LIB
 
 NDC_F32, NDC_BF16 = 0, 1
 NDC_OK = 0
-PATH_GENERIC, PATH_DEPTHWISE4 = 0, 1
+PATH_GENERIC, PATH_DEPTHWISE4, PATH_DEPTHWISE4_ROWS = 0, 1, 2
 STATIC_WORKSPACE_BYTES = 16 * 1024 * 1024
 FLAG_FORCE_GENERIC = 1
 

@@ -68,7 +68,9 @@ int check_ptr(const void* p, const char* name, int dtype) {
 
 int path_of(const NdcDesc* d) {
     if (d->flags & NDC_FLAG_FORCE_GENERIC) return NDC_PATH_GENERIC;
-    return ndc::dw4::covers(ndc::make_geo(*d, false)) ? NDC_PATH_DEPTHWISE4 : NDC_PATH_GENERIC;
+    const ndc::Geo g = ndc::make_geo(*d, false);
+    if (!ndc::dw4::covers(g)) return NDC_PATH_GENERIC;
+    return ndc::dw4::rows_class(g) ? NDC_PATH_DEPTHWISE4_ROWS : NDC_PATH_DEPTHWISE4;
 }
 
 }  // namespace
@@ -114,7 +116,7 @@ int ndc_fwd(const NdcDesc* desc, const void* x, const void* z, const float* h, c
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
     typedef __nv_bfloat16 bf16;
-    if (path_of(desc) == NDC_PATH_DEPTHWISE4) {
+    if (path_of(desc) != NDC_PATH_GENERIC) {
         bool handled = false;
         if (desc->dtype == NDC_F32)
             e = ndc::dw4::forward<float>(g, (const float*)x, (const float*)z, h, bias, (float*)out,
@@ -138,7 +140,7 @@ int ndc_fwd(const NdcDesc* desc, const void* x, const void* z, const float* h, c
 size_t ndc_bwd_workspace_bytes(const NdcDesc* desc) {
     if (validate(desc) != NDC_OK) return 0;
     const ndc::Geo g = ndc::make_geo(*desc, false);
-    if (path_of(desc) == NDC_PATH_DEPTHWISE4) {
+    if (path_of(desc) != NDC_PATH_GENERIC) {
         ndc::dw4::BwdPlan p;
         if (ndc::dw4::plan_bwd_any(g, p)) return p.bytes;
     }
@@ -170,7 +172,7 @@ int ndc_bwd(const NdcDesc* desc, const void* x, const void* z, const void* t1, c
     const ndc::Geo g = ndc::make_geo(*desc, bias != nullptr);
     cudaStream_t st = (cudaStream_t)stream;
     cudaError_t e;
-    if (path_of(desc) == NDC_PATH_DEPTHWISE4) {
+    if (path_of(desc) != NDC_PATH_GENERIC) {
         ndc::dw4::BwdPlan p;
         if (ndc::dw4::plan_bwd_any(g, p)) {
             typedef __nv_bfloat16 bf16;

@@ -56,7 +56,22 @@ def _desc(**kw):
 def test_query_accepts_and_rejects(lib):
     path = ctypes.c_int32(-1)
     assert lib.ndc_query(_desc(), ctypes.byref(path)) == 0
-    assert path.value in (_lib.PATH_GENERIC, _lib.PATH_DEPTHWISE4)
+    assert path.value == _lib.PATH_DEPTHWISE4
+    # which family takes which geometry (host-side decision, no GPU needed)
+    img = dict(groups=32, kernel_size=(5, 5))
+    for spatial, want in [((256, 256), _lib.PATH_DEPTHWISE4_ROWS),    # the 2-D benchmark layer
+                          ((128, 128), _lib.PATH_DEPTHWISE4_ROWS),
+                          ((40, 65), _lib.PATH_DEPTHWISE4_ROWS),
+                          ((64, 64), _lib.PATH_DEPTHWISE4),           # too narrow for a row CTA
+                          ((31, 200), _lib.PATH_DEPTHWISE4),          # too few rows to march
+                          ((64, 300), _lib.PATH_GENERIC)]:            # wider than a tile
+        assert lib.ndc_query(_desc(spatial=spatial, **img), ctypes.byref(path)) == 0
+        assert path.value == want, (spatial, path.value)
+    assert lib.ndc_query(_desc(groups=4, spatial=(3, 40, 100), kernel_size=(1, 5, 5)),
+                         ctypes.byref(path)) == 0
+    assert path.value == _lib.PATH_DEPTHWISE4                         # a volume is not an image
+    assert lib.ndc_query(_desc(groups=4, m=2), ctypes.byref(path)) == 0
+    assert path.value == _lib.PATH_GENERIC                            # grouped, not depthwise
     assert lib.ndc_query(_desc(flags=_lib.FLAG_FORCE_GENERIC), ctypes.byref(path)) == 0
     assert path.value == _lib.PATH_GENERIC
     assert lib.ndc_query(_desc(kernel_size=(3, 4, 3)), None) == 1  # even kernel
