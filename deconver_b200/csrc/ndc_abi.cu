@@ -7,6 +7,7 @@
 #include "ndc_b200.h"
 #include "ndc_common.cuh"
 #include "ndc_generic.cuh"
+#define NDC_DW4_EXTERN   // the tiled kernels are compiled in ndc_dw4_inst.cu
 #include "ndc_dw4_host.cuh"
 
 namespace {

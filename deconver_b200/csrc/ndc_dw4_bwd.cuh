@@ -824,7 +824,8 @@ struct ReduceParams {
     float* gb;    // (C*4) or NULL
 };
 
-__global__ void __launch_bounds__(128) reduce_kernel(const ReduceParams P) {
+template <int NT>
+__global__ void __launch_bounds__(NT) reduce_kernel(const ReduceParams P) {
     const int c = blockIdx.x;
     const int k = threadIdx.x;       // record slot
     const bool is_w = k < P.KT * SCH, is_b = k >= kPartialStride - SCH;

@@ -22,6 +22,9 @@ template <> struct FwdShape<1, 3, 3> { static constexpr int NT = 256, MAXZ = 1, 
 // so nothing is recomputed between row bands and the loads of the next row overlap the work
 // on this one.  A CTA is as wide as one row has 4-voxel strips.
 template <int NT_> struct FwdRows { static constexpr int NT = NT_, MAXZ = 4, MAXX = 1, MINB = 384 / NT_; };
+// Small volumes (3x3x3): a 256-thread CTA would mostly idle on a band of 32, 16 or 8 short rows,
+// so narrower CTAs are used where they cover the same band (more CTAs per SM instead).
+template <int NT_> struct FwdSmall { static constexpr int NT = NT_, MAXZ = 5, MAXX = 1, MINB = 512 / NT_; };
 
 inline bool shape_supported(int kD, int kH, int kW) {
     return (kD == 3 && kH == 3 && kW == 3) || (kD == 1 && kH == 5 && kW == 5) ||
@@ -106,7 +109,7 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
     const bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
                      aligned_for_vec(out, dtype) && aligned_for_vec(t1, dtype);
     // widths that occur in the published configurations get kernels with a compile-time width
-    if constexpr (KD > 1 && KH > 1) {
+    if constexpr (KD > 1 && KH > 1 && S::NT == 256) {
         if (vec && g.W == 64) return launch_fwd<T, KD, KH, KW, S, true, 16>(P, smem, BC, st);
         if (vec && g.W == 128) return launch_fwd<T, KD, KH, KW, S, true, 32>(P, smem, BC, st);
     }
@@ -127,6 +130,13 @@ struct BwdBands {
 // Rows: one-row planes of NQ 4-voxel strips (2-D images run as volumes, see FwdRows).
 template <int NQ_> struct BwdRows {
     static constexpr int RatioNT = NQ_, RatioMAXX = 1, KconvNT = 2 * NQ_, GzNT = NQ_, GzMAXX = 1;
+};
+// Small volumes (3x3x3): narrower CTAs where they cover the same bands (see FwdSmall).
+struct BwdSmall16 {   // bands of up to 64 strips of 4 (16 x 16 rows)
+    static constexpr int RatioNT = 64, RatioMAXX = 2, KconvNT = 128, GzNT = 64, GzMAXX = 2;
+};
+struct BwdSmall8 {    // bands of up to 32 strips of 4 (8 x 8 rows)
+    static constexpr int RatioNT = 32, RatioMAXX = 1, KconvNT = 32, GzNT = 32, GzMAXX = 1;
 };
 constexpr int kGzCS = 1;        // channel split of gz_kernel (2 was measured no faster)
 
@@ -185,6 +195,7 @@ struct BwdPlan {
     size_t off_gnum, off_gden, off_gt1, off_gxtmp, off_pa, off_pa2, off_pb, bytes;
     long long n_ratio, n_kconv, n_gz;   // CTAs (kconv: per tensor; = partial records)
     int rows;                           // 0: band kernels; else the rows class planned
+    int small;                          // 0, or the small-volume class planned (16 or 8)
 };
 
 template <int KD, int KH, int KW, typename S>
@@ -233,9 +244,22 @@ inline Geo as_rows(const Geo& g) {
 }
 
 inline bool plan_bwd_any(const Geo& g, BwdPlan& p) {
-    p.rows = 0;
+    p.rows = 0; p.small = 0;
     if (g.m != 1 || g.sc != SCH) return false;
-    if (g.kD == 3 && g.kH == 3 && g.kW == 3) return plan_bwd<3, 3, 3, BwdBands>(g, p);
+    if (g.kD == 3 && g.kH == 3 && g.kW == 3) {
+        BwdPlan p0;
+        if (!plan_bwd<3, 3, 3, BwdBands>(g, p0)) return false;
+        auto same_bands = [&](const BwdPlan& q) {
+            return q.ratio.nth == p0.ratio.nth && q.kconv.nth == p0.kconv.nth && q.gz.nth == p0.gz.nth;
+        };
+        p.small = 8;
+        if (plan_bwd<3, 3, 3, BwdSmall8>(g, p) && same_bands(p)) return true;
+        p.small = 16;
+        if (plan_bwd<3, 3, 3, BwdSmall16>(g, p) && same_bands(p)) return true;
+        p = p0;
+        p.rows = 0; p.small = 0;
+        return true;
+    }
     if (g.kD == 1 && g.kH == 5 && g.kW == 5) {
         const int rc = rows_class(g);
         p.rows = rc;
@@ -335,7 +359,7 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.ctas_per_bc_b = (long long)p.gz.ndc * p.gz.nth;
         P.b_has_w = gh ? 1 : 0;
         P.B = g.B; P.C = g.G; P.KT = g.KT; P.gh = gh; P.gb = gb;
-        reduce_kernel<<<g.G, 128, 0, st>>>(P);
+        reduce_kernel<kPartialStride><<<g.G, kPartialStride, 0, st>>>(P);
         launched();
     }
     return cudaGetLastError();
@@ -350,7 +374,7 @@ cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* 
     if (gx) vec = vec && aligned_for_vec(gx, dtype);
     if (gz) vec = vec && aligned_for_vec(gz, dtype);
     // widths that occur in the published configurations get kernels with a compile-time width
-    if constexpr (KD > 1 && KH > 1) {
+    if constexpr (KD > 1 && KH > 1 && S::RatioNT == 128) {
         if (vec && g.W == 64)
             return backward_launch<T, KD, KH, KW, S, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
         if (vec && g.W == 128)
@@ -369,8 +393,13 @@ template <typename T>
 cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                      const float* h, const float* bias, const T* gout, T* gx, T* gz, float* gh,
                      float* gb, void* ws, int dtype, cudaStream_t st) {
-    if (g.kD == 3)
+    if (g.kD == 3) {
+        if (p.small == 8)
+            return backward_shape<T, 3, 3, 3, BwdSmall8>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+        if (p.small == 16)
+            return backward_shape<T, 3, 3, 3, BwdSmall16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
         return backward_shape<T, 3, 3, 3, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    }
     if (g.kH == 5) {
         if (p.rows == 64)
             return backward_shape<T, 5, 1, 5, BwdRows<64>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
@@ -379,6 +408,18 @@ cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, con
         return backward_shape<T, 1, 5, 5, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
     }
     return backward_shape<T, 1, 3, 3, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+}
+
+// Narrowest forward CTA (threads) that still covers a 3x3x3 volume with as few bands as the
+// 256-thread one; 256 if none does.
+inline int fwd_small_class(const Geo& g) {
+    const long long BC = (long long)g.B * g.G;
+    Tiling t0, t; size_t smem;
+    if (!plan_fwd<3, 3, 3>(g.D, g.H, g.W, BC, t0, smem)) return 256;
+    if (plan_fwd<3, 3, 3, FwdSmall<32>>(g.D, g.H, g.W, BC, t, smem) && t.nth == t0.nth) return 32;
+    if (plan_fwd<3, 3, 3, FwdSmall<96>>(g.D, g.H, g.W, BC, t, smem) && t.nth == t0.nth) return 96;
+    if (plan_fwd<3, 3, 3, FwdSmall<160>>(g.D, g.H, g.W, BC, t, smem) && t.nth == t0.nth) return 160;
+    return 256;
 }
 
 // Whether the tiled kernels take this geometry (pointer alignment only affects vector width).
@@ -398,8 +439,14 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
                     T* out, T* t1, int dtype, cudaStream_t st, bool& handled) {
     handled = false;
     if (g.m != 1 || g.sc != SCH) return cudaSuccess;
-    if (g.kD == 3 && g.kH == 3 && g.kW == 3)
-        return forward_shape<T, 3, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
+    if (g.kD == 3 && g.kH == 3 && g.kW == 3) {
+        switch (fwd_small_class(g)) {
+            case 32: return forward_shape<T, 3, 3, 3, FwdSmall<32>>(g, x, z, h, bias, out, t1, dtype, st, handled);
+            case 96: return forward_shape<T, 3, 3, 3, FwdSmall<96>>(g, x, z, h, bias, out, t1, dtype, st, handled);
+            case 160: return forward_shape<T, 3, 3, 3, FwdSmall<160>>(g, x, z, h, bias, out, t1, dtype, st, handled);
+            default: return forward_shape<T, 3, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
+        }
+    }
     if (g.kD == 1 && g.kH == 5 && g.kW == 5) {
         const int rc = rows_class(g);
         if (rc) {
@@ -415,6 +462,36 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
         return forward_shape<T, 1, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
     return cudaSuccess;
 }
+
+// ---------------------------------------------------------------------------------------
+// The kernels are compiled in several translation units (ndc_dw4_inst.cu, once per part and
+// storage type) so that the build can use several host cores.  NDC_DW4_INSTANCES(PREFIX, T)
+// lists every heavy instantiation of part NDC_DW4_PART: PREFIX is `template` where they are
+// compiled and `extern template` in the translation unit that only calls them.
+#define NDC_DW4_FWD_INSTANCES(PREFIX, T)                                                      \
+    PREFIX cudaError_t forward<T>(const Geo&, const T*, const T*, const float*, const float*, \
+                                  T*, T*, int, cudaStream_t, bool&);
+#define NDC_DW4_BWD_ARGS(T)                                                                   \
+    (const Geo&, const BwdPlan&, const T*, const T*, const T*, const float*, const float*,    \
+     const T*, T*, T*, float*, float*, void*, int, cudaStream_t)
+#define NDC_DW4_BWD3D_INSTANCES(PREFIX, T)                                                    \
+    PREFIX cudaError_t backward_shape<T, 3, 3, 3, BwdBands> NDC_DW4_BWD_ARGS(T);              \
+    PREFIX cudaError_t backward_shape<T, 3, 3, 3, BwdSmall16> NDC_DW4_BWD_ARGS(T);            \
+    PREFIX cudaError_t backward_shape<T, 3, 3, 3, BwdSmall8> NDC_DW4_BWD_ARGS(T);
+#define NDC_DW4_BWD2D_INSTANCES(PREFIX, T)                                                    \
+    PREFIX cudaError_t backward_shape<T, 1, 5, 5, BwdBands> NDC_DW4_BWD_ARGS(T);              \
+    PREFIX cudaError_t backward_shape<T, 1, 3, 3, BwdBands> NDC_DW4_BWD_ARGS(T);              \
+    PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<64>> NDC_DW4_BWD_ARGS(T);           \
+    PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<32>> NDC_DW4_BWD_ARGS(T);
+
+#ifdef NDC_DW4_EXTERN
+NDC_DW4_FWD_INSTANCES(extern template, float)
+NDC_DW4_FWD_INSTANCES(extern template, __nv_bfloat16)
+NDC_DW4_BWD3D_INSTANCES(extern template, float)
+NDC_DW4_BWD3D_INSTANCES(extern template, __nv_bfloat16)
+NDC_DW4_BWD2D_INSTANCES(extern template, float)
+NDC_DW4_BWD2D_INSTANCES(extern template, __nv_bfloat16)
+#endif
 
 }  // namespace dw4
 }  // namespace ndc
