@@ -229,10 +229,10 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     return true;
 }
 
-// 2-D images of 65..256 columns are run as volumes of one-row planes (the same memory and the
-// same filter layout): returns the strips per row the kernels are built for, 0 for other shapes.
+// 2-D images (5x5 or 3x3) of 65..256 columns are run as volumes of one-row planes (the same
+// memory and the same filter layout): returns the strips per row the kernels are built for, 0 for other shapes.
 inline int rows_class(const Geo& g) {
-    if (g.D != 1 || g.kD != 1 || g.kH != 5 || g.kW != 5 || g.H < 32) return 0;
+    if (g.D != 1 || g.kD != 1 || g.kH != g.kW || (g.kH != 5 && g.kH != 3) || g.H < 32) return 0;
     if (g.W > 128 && g.W <= 256) return 64;
     if (g.W > 64 && g.W <= 128) return 32;
     return 0;
@@ -241,6 +241,17 @@ inline Geo as_rows(const Geo& g) {
     Geo v = g;
     v.D = g.H; v.H = 1; v.kD = g.kH; v.kH = 1; v.pD = g.pH; v.pH = 0;
     return v;
+}
+
+// K x K images: row kernels where rows_class allows, else band kernels.
+template <int K>
+inline bool plan_bwd_image(const Geo& g, BwdPlan& p) {
+    const int rc = rows_class(g);
+    p.rows = rc;
+    if (rc == 64 && plan_bwd<K, 1, K, BwdRows<64>>(as_rows(g), p)) return true;
+    if (rc == 32 && plan_bwd<K, 1, K, BwdRows<32>>(as_rows(g), p)) return true;
+    p.rows = 0;
+    return plan_bwd<1, K, K, BwdBands>(g, p);
 }
 
 inline bool plan_bwd_any(const Geo& g, BwdPlan& p) {
@@ -260,15 +271,8 @@ inline bool plan_bwd_any(const Geo& g, BwdPlan& p) {
         p.rows = 0; p.small = 0;
         return true;
     }
-    if (g.kD == 1 && g.kH == 5 && g.kW == 5) {
-        const int rc = rows_class(g);
-        p.rows = rc;
-        if (rc == 64 && plan_bwd<5, 1, 5, BwdRows<64>>(as_rows(g), p)) return true;
-        if (rc == 32 && plan_bwd<5, 1, 5, BwdRows<32>>(as_rows(g), p)) return true;
-        p.rows = 0;
-        return plan_bwd<1, 5, 5, BwdBands>(g, p);
-    }
-    if (g.kD == 1 && g.kH == 3 && g.kW == 3) return plan_bwd<1, 3, 3, BwdBands>(g, p);
+    if (g.kD == 1 && g.kH == 5 && g.kW == 5) return plan_bwd_image<5>(g, p);
+    if (g.kD == 1 && g.kH == 3 && g.kW == 3) return plan_bwd_image<3>(g, p);
     return false;
 }
 
@@ -388,6 +392,17 @@ cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* 
                : backward_launch<T, KD, KH, KW, S, false, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
 }
 
+template <typename T, int K>
+cudaError_t backward_image(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
+                           const float* h, const float* bias, const T* gout, T* gx, T* gz,
+                           float* gh, float* gb, void* ws, int dtype, cudaStream_t st) {
+    if (p.rows == 64)
+        return backward_shape<T, K, 1, K, BwdRows<64>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    if (p.rows == 32)
+        return backward_shape<T, K, 1, K, BwdRows<32>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    return backward_shape<T, 1, K, K, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+}
+
 // `p` must come from plan_bwd_any(g): the same rule picks the kernel family here.
 template <typename T>
 cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
@@ -400,14 +415,8 @@ cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, con
             return backward_shape<T, 3, 3, 3, BwdSmall16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
         return backward_shape<T, 3, 3, 3, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
     }
-    if (g.kH == 5) {
-        if (p.rows == 64)
-            return backward_shape<T, 5, 1, 5, BwdRows<64>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
-        if (p.rows == 32)
-            return backward_shape<T, 5, 1, 5, BwdRows<32>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
-        return backward_shape<T, 1, 5, 5, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
-    }
-    return backward_shape<T, 1, 3, 3, BwdBands>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    if (g.kH == 5) return backward_image<T, 5>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
+    return backward_image<T, 3>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
 }
 
 // Narrowest forward CTA (threads) that still covers a 3x3x3 volume with as few bands as the
@@ -434,6 +443,20 @@ inline bool covers(const Geo& g) {
     return plan_fwd<1, 3, 3>(g.D, g.H, g.W, BC, t, smem);
 }
 
+template <typename T, int K>
+cudaError_t forward_image(const Geo& g, const T* x, const T* z, const float* h, const float* bias,
+                          T* out, T* t1, int dtype, cudaStream_t st, bool& handled) {
+    const int rc = rows_class(g);
+    if (rc) {
+        const Geo v = as_rows(g);
+        cudaError_t e = rc == 64
+            ? forward_shape<T, K, 1, K, FwdRows<64>>(v, x, z, h, bias, out, t1, dtype, st, handled)
+            : forward_shape<T, K, 1, K, FwdRows<32>>(v, x, z, h, bias, out, t1, dtype, st, handled);
+        if (handled || e != cudaSuccess) return e;
+    }
+    return forward_shape<T, 1, K, K>(g, x, z, h, bias, out, t1, dtype, st, handled);
+}
+
 template <typename T>
 cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const float* bias,
                     T* out, T* t1, int dtype, cudaStream_t st, bool& handled) {
@@ -447,19 +470,10 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
             default: return forward_shape<T, 3, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
         }
     }
-    if (g.kD == 1 && g.kH == 5 && g.kW == 5) {
-        const int rc = rows_class(g);
-        if (rc) {
-            const Geo v = as_rows(g);
-            cudaError_t e = rc == 64
-                ? forward_shape<T, 5, 1, 5, FwdRows<64>>(v, x, z, h, bias, out, t1, dtype, st, handled)
-                : forward_shape<T, 5, 1, 5, FwdRows<32>>(v, x, z, h, bias, out, t1, dtype, st, handled);
-            if (handled || e != cudaSuccess) return e;
-        }
-        return forward_shape<T, 1, 5, 5>(g, x, z, h, bias, out, t1, dtype, st, handled);
-    }
+    if (g.kD == 1 && g.kH == 5 && g.kW == 5)
+        return forward_image<T, 5>(g, x, z, h, bias, out, t1, dtype, st, handled);
     if (g.kD == 1 && g.kH == 3 && g.kW == 3)
-        return forward_shape<T, 1, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
+        return forward_image<T, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
     return cudaSuccess;
 }
 
@@ -482,7 +496,9 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
     PREFIX cudaError_t backward_shape<T, 1, 5, 5, BwdBands> NDC_DW4_BWD_ARGS(T);              \
     PREFIX cudaError_t backward_shape<T, 1, 3, 3, BwdBands> NDC_DW4_BWD_ARGS(T);              \
     PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<64>> NDC_DW4_BWD_ARGS(T);           \
-    PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<32>> NDC_DW4_BWD_ARGS(T);
+    PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<32>> NDC_DW4_BWD_ARGS(T);           \
+    PREFIX cudaError_t backward_shape<T, 3, 1, 3, BwdRows<64>> NDC_DW4_BWD_ARGS(T);           \
+    PREFIX cudaError_t backward_shape<T, 3, 1, 3, BwdRows<32>> NDC_DW4_BWD_ARGS(T);
 
 #ifdef NDC_DW4_EXTERN
 NDC_DW4_FWD_INSTANCES(extern template, float)

@@ -67,6 +67,8 @@ def test_query_accepts_and_rejects(lib):
                           ((64, 300), _lib.PATH_GENERIC)]:            # wider than a tile
         assert lib.ndc_query(_desc(spatial=spatial, **img), ctypes.byref(path)) == 0
         assert path.value == want, (spatial, path.value)
+    assert lib.ndc_query(_desc(groups=4, spatial=(128, 128), kernel_size=(3, 3)), ctypes.byref(path)) == 0
+    assert path.value == _lib.PATH_DEPTHWISE4_ROWS
     assert lib.ndc_query(_desc(groups=4, spatial=(3, 40, 100), kernel_size=(1, 5, 5)),
                          ctypes.byref(path)) == 0
     assert path.value == _lib.PATH_DEPTHWISE4                         # a volume is not an image
@@ -108,3 +110,34 @@ def test_rank_padding():
         _lib.make_desc(1, 4, 1, 4, (2, 2, 2, 2), (3, 3, 3, 3), 0.0, True, 0)
     with pytest.raises(ValueError):
         _lib.make_desc(1, 4, 1, 4, (9, 8), (3,), 0.0, True, 0)
+
+
+def test_planner_on_random_geometries(lib):
+    """Host-side planning (kernel family, tiling, workspace size) over a seeded sweep of
+    geometries, including degenerate and very large ones: every query answers, the workspace
+    is bounded by the scratch tensors the backward needs, and repeated queries agree."""
+    import numpy as np
+
+    rng = np.random.default_rng(7)
+    path = ctypes.c_int32(-1)
+    kernels = [(3, 3, 3), (5, 5), (3, 3), (1, 5, 5), (7,), (5, 5, 5), (3, 5)]
+    for _ in range(400):
+        ks = kernels[int(rng.integers(len(kernels)))]
+        hi = {1: 5000, 2: 700, 3: 200}[len(ks)]
+        spatial = tuple(int(rng.integers(1, hi)) for _ in ks)
+        batch, groups = int(rng.integers(1, 33)), int(2 ** rng.integers(0, 10))
+        m, sc = (1, 4) if rng.random() < 0.8 else (int(rng.integers(1, 5)), int(rng.integers(1, 9)))
+        elems = batch * groups * int(np.prod(spatial))
+        if elems * max(m, sc) >= 2 ** 40:
+            continue
+        d = _desc(batch=batch, groups=groups, m=m, sc=sc, spatial=spatial, kernel_size=ks)
+        assert lib.ndc_query(d, ctypes.byref(path)) == 0, (batch, groups, m, sc, spatial, ks)
+        assert path.value in (_lib.PATH_GENERIC, _lib.PATH_DEPTHWISE4, _lib.PATH_DEPTHWISE4_ROWS)
+        if (m, sc) != (1, 4) or ks in [(7,), (5, 5, 5), (3, 5)]:
+            assert path.value == _lib.PATH_GENERIC
+        need = lib.ndc_bwd_workspace_bytes(d)
+        assert need == lib.ndc_bwd_workspace_bytes(d)
+        # gnum, gden (float32, source-sized), gt1 and a spare input-sized tensor, plus the
+        # per-CTA records of the filter-gradient reduction (a few percent at most)
+        bound = int(4 * elems * (2 * sc + 2 * m) * 1.05) + 64 * 1024 * 1024 + 4096 * batch * groups
+        assert 0 < need <= bound, (need, bound, batch, groups, m, sc, spatial, ks)

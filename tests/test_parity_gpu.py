@@ -333,11 +333,12 @@ def test_tiled_kernels_match_generic_kernels_on_random_geometries(dev):
                       bool(rng.random() < 0.7)))
     cases += [(1, 2, (3, 3, 3), (70, 3, 8), True), (1, 1, (3, 3, 3), (5, 64, 64), True),
               (1, 1, (5, 5), (64, 256), False), (2, 3, (3, 3), (33, 256), True),
-              # 5x5 images of 65..256 columns run row by row: ragged widths of both CTA sizes,
+              # 5x5 and 3x3 images of 65..256 columns run row by row: ragged widths of both CTA sizes,
               # fewer rows than one chunk, chunk tails, the narrowest and the shortest image taken
               (1, 2, (5, 5), (33, 67), True), (2, 1, (5, 5), (100, 129), True),
               (1, 1, (5, 5), (45, 255), False), (1, 1, (5, 5), (300, 128), True),
               (1, 3, (5, 5), (32, 65), True), (1, 1, (5, 5), (31, 200), True),
+              (1, 2, (3, 3), (40, 100), True), (2, 1, (3, 3), (70, 131), False),
               # a volume with a flat 1x5x5 kernel is not an image: stays on the band kernels
               (1, 2, (1, 5, 5), (3, 40, 100), True)]
     for B, C, ks, spatial, relu in cases:
