@@ -309,7 +309,7 @@ def run_b200(args):
         e2e_step()
     s_main.wait_event(out_done)
     barrier()
-    e2e_steps = max(1, min(args.steps, 10))
+    e2e_steps = max(1, min(args.steps, 40))   # enough steps that pipeline fill and drain stay small
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
