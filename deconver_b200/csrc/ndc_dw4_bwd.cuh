@@ -82,27 +82,34 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t, 2, 0);
     const int tid = threadIdx.x;
-    const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch, H = P.H,
+    constexpr bool ROWS = KD > 1 && KH == 1;   // images of a batch as the rows of one volume
+    const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch,
               W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
-    const long long HW = (long long)H * W, SP = HW * D;
+    const SlabAddr<ROWS> addr(P.C, D, P.H, W);
+    const long long HW = addr.plane, SP = addr.chan;
+    const long long RWX = ROWS ? addr.row_x : W, RWZ = ROWS ? addr.row_z : W;
 
     int blk = blockIdx.x;
     const int th = blk % P.t.nth; blk /= P.t.nth;
     const int dch = blk % P.t.ndc; blk /= P.t.ndc;
     const int bc = blk;
     const int c = bc % P.C;
-    const int h0 = th * P.t.TH;
-    const int TH = min(P.t.TH, H - h0);
+    const int h_band = th * P.t.TH;
+    const int TH = min(P.t.TH, P.H - h_band);
     const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
     const int RT = lay.RT;
+    // rows mode: the band is folded into the base pointers and rows are counted from it
+    const int h0 = ROWS ? 0 : h_band, H = ROWS ? P.H - h_band : P.H;
+    const long long bx = (long long)bc * SP + (ROWS ? h_band * RWX : 0);
+    const long long bz = (long long)bc * SCH * SP + (ROWS ? h_band * RWZ : 0);
 
-    const T* xg = reinterpret_cast<const T*>(P.x) + (long long)bc * SP;
-    const T* tg = reinterpret_cast<const T*>(P.t1) + (long long)bc * SP;
-    const T* zg = reinterpret_cast<const T*>(P.z) + (long long)bc * SCH * SP;
-    const T* gg = reinterpret_cast<const T*>(P.gout) + (long long)bc * SCH * SP;
-    float* gng = P.gnum + (long long)bc * SCH * SP;
-    float* gdg = P.gden + (long long)bc * SCH * SP;
-    T* dirg = P.gz ? reinterpret_cast<T*>(P.gz) + (long long)bc * SCH * SP : nullptr;
+    const T* xg = reinterpret_cast<const T*>(P.x) + bx;
+    const T* tg = reinterpret_cast<const T*>(P.t1) + bx;
+    const T* zg = reinterpret_cast<const T*>(P.z) + bz;
+    const T* gg = reinterpret_cast<const T*>(P.gout) + bz;
+    float* gng = P.gnum + bz;
+    float* gdg = P.gden + bz;
+    T* dirg = P.gz ? reinterpret_cast<T*>(P.gz) + bz : nullptr;
 
     float* wA = smem + lay.wA;
     float* xring = smem + lay.ring0;
@@ -115,7 +122,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
         for (int i = tid; i < KT * SCH; i += NT) wA[i] = hc[(i % SCH) * KT + i / SCH];  // [tau][j]
     }
     const int nx = RT * NQ;
-    if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
+    if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, RWX, NT);
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
@@ -131,7 +138,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
             const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
             if (h < 0 || h >= H) continue;
             stage_chunk<PW, false>(dst, (r * pitch) | (w << 16) | (n << 26),
-                                   load4<T, VEC>(src + (long long)h * W + w, n));
+                                   load4<T, VEC>(src + h * RWX + w, n));
         }
     };
     // prologue: planes d0-PD .. d0+PD
@@ -162,7 +169,7 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
         for (int item = tid; item < items; item += NT) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
-            const long long off = (long long)d * HW + (long long)hrow * W;
+            const long long off = (long long)d * HW + hrow * RWZ;
             // global strips first: their latency hides behind the tap sweep
             Raw4<T> zraw[SCH], graw[SCH];   // converted in the epilogue
 #pragma unroll
@@ -289,9 +296,12 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
     const int tid = threadIdx.x;
+    constexpr bool ROWS = KD > 1 && KH == 1;   // images of a batch as the rows of one volume
     const int NQ = WQ ? WQ : P.t.NQ, NS8 = (NQ + 1) / 2, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch,
-              H = P.H, W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
-    const long long HW = (long long)H * W, SP = HW * D;
+              W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
+    const SlabAddr<ROWS> addr(P.C, D, P.H, W);
+    const long long HW = addr.plane, SP = addr.chan;
+    const long long RWX = ROWS ? addr.row_x : W, RWZ = ROWS ? addr.row_z : W;
     const int which = blockIdx.y;
 
     int blk = blockIdx.x;
@@ -299,15 +309,19 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
     const int dch = blk % P.t.ndc; blk /= P.t.ndc;
     const int bc = blk;
     const int c = bc % P.C;
-    const int h0 = th * P.t.TH;
-    const int TH = min(P.t.TH, H - h0);
+    const int h_band = th * P.t.TH;
+    const int TH = min(P.t.TH, P.H - h_band);
     const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
     const int RS = lay.RS;
+    // rows mode: the band is folded into the base pointers and rows are counted from it
+    const int h0 = ROWS ? 0 : h_band, H = ROWS ? P.H - h_band : P.H;
+    const long long bx = (long long)bc * SP + (ROWS ? h_band * RWX : 0);
+    const long long bz = (long long)bc * SCH * SP + (ROWS ? h_band * RWZ : 0);
 
-    const float* ing = P.in[which] + (long long)bc * SCH * SP;
-    float* outf = P.out_is_f32[which] ? reinterpret_cast<float*>(P.out[which]) + (long long)bc * SP : nullptr;
-    T* outt = P.out_is_f32[which] ? nullptr : reinterpret_cast<T*>(P.out[which]) + (long long)bc * SP;
-    const T* auxg = WGRAD ? reinterpret_cast<const T*>(P.aux[which]) + (long long)bc * SP : nullptr;
+    const float* ing = P.in[which] + bz;
+    float* outf = P.out_is_f32[which] ? reinterpret_cast<float*>(P.out[which]) + bx : nullptr;
+    T* outt = P.out_is_f32[which] ? nullptr : reinterpret_cast<T*>(P.out[which]) + bx;
+    const T* auxg = WGRAD ? reinterpret_cast<const T*>(P.aux[which]) + bx : nullptr;
 
     float* wK = smem + lay.wK;
     float* sbuf = smem + lay.sbuf;
@@ -329,7 +343,7 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
         const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
         const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
         ChunkDesc dsc;
-        dsc.goff = (h < 0 || h >= H) ? -1 : (int)(ch * SP) + h * W + w;
+        dsc.goff = (h < 0 || h >= H) ? -1 : (int)(ch * SP + h * RWZ) + w;
         dsc.soff = ((ch * RS + r) * pitch + (phys_quad<true>(c4 + 1) << 2)) | (n << 26);
         desc[id] = dsc;
     }
@@ -421,7 +435,7 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
         }
         if (row >= 0) {
             const int w0 = VK * strip + (hi ? 4 : 0) + (odd ? 2 : 0);
-            const long long off = (long long)q * HW + (long long)(h0 + row) * W + w0;
+            const long long off = (long long)q * HW + (h0 + row) * RWX + w0;
             if (VEC) {
                 if (w0 < W) {
                     if (outf) *reinterpret_cast<float2*>(outf + off) = make_float2(o2[0], o2[1]);
@@ -458,7 +472,7 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
             for (int v = 0; v < VK; ++v) kacc[a][v] = 0.0f;
         // strip of plane q of the aux tensor, zero outside the chunk; the row/column part of the
         // address is fixed per thread
-        const T* aux_row = WGRAD ? auxg + (long long)(h0 + k_row) * W : nullptr;
+        const T* aux_row = WGRAD ? auxg + (h0 + k_row) * RWX : nullptr;
         auto aux_raw = [&](int q, Raw4<T> (&dst)[2]) {
             if (k_ok && q >= d0 && q < d1) {
                 dst[0] = load_strip_raw<T, VEC>(aux_row + (long long)q * HW, VK * k_strip, W);
@@ -531,7 +545,7 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
 #pragma unroll
                 for (int v = 0; v < VK; ++v) { acc[0][v] = 0.0f; aux[0][v] = 0.0f; }
                 if (WGRAD && ok)
-                    load_strip_global<T, VEC, VK>(auxg + (long long)p * HW + (long long)(h0 + row) * W,
+                    load_strip_global<T, VEC, VK>(auxg + (long long)p * HW + (h0 + row) * RWX,
                                                   VK * strip, W, aux[0]);
                 if (ok) accumulate(std::integral_constant<int, 0>{}, p, row, strip, acc, aux);
                 finish(p, ok ? row : -1, strip, acc[0]);
@@ -592,23 +606,30 @@ __global__ void __launch_bounds__(NT, CS == 2 ? 512 / NT : 256 / NT) gz_kernel(c
     const L lay(P.t, 1, gz_combine_floats<KD, KH, KW, CS>(NT));
     const int tid = threadIdx.x;
     const int part = tid % CS;            // which channels: part*CH .. part*CH + CH-1
-    const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch, H = P.H,
+    constexpr bool ROWS = KD > 1 && KH == 1;   // images of a batch as the rows of one volume
+    const int NQ = WQ ? WQ : P.t.NQ, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch,
               W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
-    const long long HW = (long long)H * W, SP = HW * D;
+    const SlabAddr<ROWS> addr(P.C, D, P.H, W);
+    const long long HW = addr.plane, SP = addr.chan;
+    const long long RWX = ROWS ? addr.row_x : W, RWZ = ROWS ? addr.row_z : W;
 
     int blk = blockIdx.x;
     const int th = blk % P.t.nth; blk /= P.t.nth;
     const int dch = blk % P.t.ndc; blk /= P.t.ndc;
     const int bc = blk;
     const int c = bc % P.C;
-    const int h0 = th * P.t.TH;
-    const int TH = min(P.t.TH, H - h0);
+    const int h_band = th * P.t.TH;
+    const int TH = min(P.t.TH, P.H - h_band);
     const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
     const int RT = lay.RT;
+    // rows mode: the band is folded into the base pointers and rows are counted from it
+    const int h0 = ROWS ? 0 : h_band, H = ROWS ? P.H - h_band : P.H;
+    const long long bx = (long long)bc * SP + (ROWS ? h_band * RWX : 0);
+    const long long bz = ((long long)bc * SCH + part * CH) * SP + (ROWS ? h_band * RWZ : 0);
 
-    const float* tg = P.gt1 + (long long)bc * SP;
-    const T* zg = reinterpret_cast<const T*>(P.z) + ((long long)bc * SCH + part * CH) * SP;
-    T* gzg = P.gz ? reinterpret_cast<T*>(P.gz) + ((long long)bc * SCH + part * CH) * SP : nullptr;
+    const float* tg = P.gt1 + bx;
+    const T* zg = reinterpret_cast<const T*>(P.z) + bz;
+    T* gzg = P.gz ? reinterpret_cast<T*>(P.gz) + bz : nullptr;
 
     float* wA = smem + lay.wA;
     float* ring = smem + lay.ring0;
@@ -619,7 +640,7 @@ __global__ void __launch_bounds__(NT, CS == 2 ? 512 / NT : 256 / NT) gz_kernel(c
         for (int i = tid; i < KT * SCH; i += NT) wA[i] = hc[(i % SCH) * KT + i / SCH];
     }
     const int nx = RT * NQ;
-    if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
+    if (KD > 1) build_descs(desc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, RWX, NT);
     float bj[CH];
 #pragma unroll
     for (int j = 0; j < CH; ++j) bj[j] = P.bias ? P.bias[c * SCH + part * CH + j] : 0.0f;
@@ -643,7 +664,7 @@ __global__ void __launch_bounds__(NT, CS == 2 ? 512 / NT : 256 / NT) gz_kernel(c
             const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
             if (h < 0 || h >= H) continue;
             stage_chunk<PW, false>(dst, (r * pitch) | (w << 16) | (n << 26),
-                                   load4<float, VEC>(src + (long long)h * W + w, n));
+                                   load4<float, VEC>(src + h * RWX + w, n));
         }
     };
     for (int q = d0 - PD; q <= d0 + PD; ++q)
@@ -657,7 +678,7 @@ __global__ void __launch_bounds__(NT, CS == 2 ? 512 / NT : 256 / NT) gz_kernel(c
     constexpr int NSTR = 2 * CH;
     StripFetcher<T, VEC, NSTR, NT> fetch(smem + lay.total_floats);
     auto strip_ptrs = [&](int d, int item, const T* (&ptr)[NSTR]) {
-        const long long off = (long long)d * HW + (long long)(h0 + item / NQ) * W + VA * (item % NQ);
+        const long long off = (long long)d * HW + (h0 + item / NQ) * RWZ + VA * (item % NQ);
 #pragma unroll
         for (int j = 0; j < CH; ++j) {
             ptr[j] = zg + j * SP + off;
@@ -688,7 +709,7 @@ __global__ void __launch_bounds__(NT, CS == 2 ? 512 / NT : 256 / NT) gz_kernel(c
         for (int item = slot0; item < items; item += NSLOT) {
             const int a_row = item / NQ, a_q = item % NQ;
             const int hrow = h0 + a_row, w0 = VA * a_q;
-            const long long off = (long long)d * HW + (long long)hrow * W;
+            const long long off = (long long)d * HW + hrow * RWZ;
             float strips[NSTR][VA];
             {
                 const T* ptr[NSTR];

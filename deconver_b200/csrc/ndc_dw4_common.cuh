@@ -204,6 +204,28 @@ __device__ __forceinline__ void store_strip_global(T* row, int w0, int W, const 
     }
 }
 
+// Global-memory strides (in elements) of the slab a CTA works on.
+//   Volumes (and images handled band by band): channel-major planes of H x W, one (sample,
+//   group) pair per slab: plane stride H*W, channel stride D*H*W, row stride W.
+//   Rows mode (kernel K x 1 x K, see the host side): a 2-D batch is addressed as ONE volume per
+//   group whose planes are the image rows and whose plane rows are the images of the batch
+//   (kernel height 1: they never mix).  Plane stride W, channel stride D*W (one image), row
+//   stride = one sample (C channels of x-like tensors, 4*C of z-like ones).  The CTA's band of
+//   images is folded into its base pointers, so rows are counted from the band's first image.
+template <bool ROWS>
+struct SlabAddr {
+    long long plane, chan, row_x, row_z;
+    __device__ __forceinline__ SlabAddr(int C, int D, int H, int W) {
+        if (ROWS) {
+            plane = W; chan = (long long)D * W;
+            row_x = chan * C; row_z = row_x * SCH;
+        } else {
+            plane = (long long)H * W; chan = plane * D;
+            row_x = W; row_z = W;
+        }
+    }
+};
+
 // Plane loader.  A plane region of `rows` rows is cut into chunks of 4 consecutive elements;
 // chunk -> (channel, row, quad) decoding is done once per CTA into a descriptor table in
 // shared memory: .goff = element offset inside the plane (or -1 for a row outside the
@@ -217,7 +239,7 @@ __device__ __forceinline__ int desc_ch(int soff) { return (soff >> 29) & 3; }
 
 __device__ __forceinline__ void build_descs(ChunkDesc* tab, int channels, int rows, int NQ,
                                             int pitch, int h_first, int H, int W, long long SP,
-                                            int nthreads) {
+                                            long long row_stride, int nthreads) {
     const int total = channels * rows * NQ;
     for (int id = threadIdx.x; id < total; id += nthreads) {
         const int c4 = id % NQ;
@@ -229,7 +251,7 @@ __device__ __forceinline__ void build_descs(ChunkDesc* tab, int channels, int ro
         if (h < 0 || h >= H) {
             d.goff = -1; d.soff = 0;
         } else {
-            d.goff = (int)(ch * SP) + h * W + w;
+            d.goff = (int)(ch * SP + h * row_stride) + w;
             d.soff = ((ch * rows + r) * pitch) | (w << 16) | ((n < 4 ? n : 4) << 26) | (ch << 29);
         }
         tab[id] = d;

@@ -70,9 +70,12 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t);
     const int tid = threadIdx.x;
+    constexpr bool ROWS = KD > 1 && KH == 1;   // images of a batch as the rows of one volume
     const int NQ = WQ ? WQ : P.t.NQ, NS8 = (NQ + 1) / 2, pitch = WQ ? row_pitch(4 * WQ) : P.t.pitch,
-              H = P.H, W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
-    const long long HW = (long long)H * W, SP = HW * D;
+              W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
+    const SlabAddr<ROWS> addr(P.C, D, P.H, W);
+    const long long HW = addr.plane, SP = addr.chan;
+    const long long RWX = ROWS ? addr.row_x : W, RWZ = ROWS ? addr.row_z : W;
 
     // ---- which work item
     int blk = blockIdx.x;
@@ -80,15 +83,19 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     const int dch = blk % P.t.ndc; blk /= P.t.ndc;
     const int bc = blk;                 // b * C + c
     const int c = bc % P.C;
-    const int h0 = th * P.t.TH;
-    const int TH = min(P.t.TH, H - h0);
+    const int h_band = th * P.t.TH;     // first row of this CTA's band
+    const int TH = min(P.t.TH, P.H - h_band);
     const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
     const int RS = lay.RS, RT = lay.RT;
+    // rows mode: the band is folded into the base pointers and rows are counted from it
+    const int h0 = ROWS ? 0 : h_band, H = ROWS ? P.H - h_band : P.H;
+    const long long bx = (long long)bc * SP + (ROWS ? h_band * RWX : 0);
+    const long long bz = (long long)bc * SCH * SP + (ROWS ? h_band * RWZ : 0);
 
-    const T* xg = reinterpret_cast<const T*>(P.x) + (long long)bc * SP;
-    const T* zg = reinterpret_cast<const T*>(P.z) + (long long)bc * SCH * SP;
-    T* og = reinterpret_cast<T*>(P.out) + (long long)bc * SCH * SP;
-    T* tg = reinterpret_cast<T*>(P.t1) + (long long)bc * SP;
+    const T* xg = reinterpret_cast<const T*>(P.x) + bx;
+    const T* zg = reinterpret_cast<const T*>(P.z) + bz;
+    T* og = reinterpret_cast<T*>(P.out) + bz;
+    T* tg = reinterpret_cast<T*>(P.t1) + bx;
 
     float* wA = smem + lay.wA;
     float* wK = smem + lay.wK;
@@ -122,7 +129,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
     auto z_soff = [&](int ch, int r, int c4, int n) {
         return ((ch * RS + r) * pitch + (phys_quad<true>(c4 + 1) << 2)) | (n << 26) | (ch << 29);
     };
-    if (KD > 1) build_descs(xdesc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, NT);
+    if (KD > 1) build_descs(xdesc, 1, RT, NQ, pitch, h0 - PH, H, W, SP, RWX, NT);
     float bj[SCH];
 #pragma unroll
     for (int j = 0; j < SCH; ++j) bj[j] = P.bias ? P.bias[c * SCH + j] : 0.0f;
@@ -138,7 +145,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
         if (KD > 1 && id < nz) {
             const int c4 = id % NQ, t = id / NQ, r = t % RS, ch = t / RS;
             const int h = h0 - 2 * PH + r, w = 4 * c4;
-            if (h >= 0 && h < H) zg_off[i] = (int)(ch * SP) + h * W + w;
+            if (h >= 0 && h < H) zg_off[i] = (int)(ch * SP + h * RWZ) + w;
             zs_off[i] = z_soff(ch, r, c4, min(4, W - w));
             zb[i] = ch == 0 ? bj[0] : ch == 1 ? bj[1] : ch == 2 ? bj[2] : bj[3];
         }
@@ -220,7 +227,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int h = h0 - 2 * PH + r, w = 4 * c4, n = min(4, W - w);
             if (h < 0 || h >= H) continue;
             const int soff = z_soff(ch, r, c4, n);
-            const float4 v = load4<T, VEC>(src + ch * SP + (long long)h * W + w, n);
+            const float4 v = load4<T, VEC>(src + ch * SP + h * RWZ + w, n);
             const float b = ch == 0 ? bj[0] : ch == 1 ? bj[1] : ch == 2 ? bj[2] : bj[3];
             *reinterpret_cast<float4*>(dst + (soff & 0x3ffffff)) = rectify(v, b, n);
         }
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             const int h = h0 - PH + r, w = 4 * c4, n = min(4, W - w);
             if (h < 0 || h >= H) continue;
             const int soff = (r * pitch) | (w << 16) | (n << 26);
-            stage_chunk<PW, false>(dst, soff, load4<T, VEC>(src + (long long)h * W + w, n));
+            stage_chunk<PW, false>(dst, soff, load4<T, VEC>(src + h * RWX + w, n));
         }
     };
     const int qbase = d0 - 3 * PD - 1;  // ring slot of plane q is (q - qbase) % RING
@@ -310,7 +317,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             store_strip<VA, PW, false>(t1ring + slot_of(qdone) * lay.plane_t + row * pitch, w0, tv);
             const int h = h0 - PH + row;
             if (qdone >= d0 && qdone < d1 && row >= PH && row < PH + TH)
-                store_strip_global<T, VEC, VA>(tg + (long long)qdone * HW + (long long)h * W, w0, W, tv);
+                store_strip_global<T, VEC, VA>(tg + (long long)qdone * HW + h * RWX, w0, W, tv);
         };
         if (KD > 1) {
             if (k_ok && s_ok) k_accumulate(k_row, k_strip, kacc);
@@ -355,7 +362,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             Raw4<T> zraw[SCH];   // converted in the epilogue, after the tap sweep
 #pragma unroll
             for (int j = 0; j < SCH; ++j)
-                zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + (long long)d * HW + (long long)hrow * W, w0, W);
+                zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + (long long)d * HW + hrow * RWZ, w0, W);
             // accumulators hold channel pairs (2jp, 2jp+1) of one voxel
             f32x2 an[SCH / 2][VA], ad[SCH / 2][VA];
             {
@@ -388,7 +395,7 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
                     if (P.relu) s = fmaxf(s, 0.0f);
                     ov[v] = fast_div(s * lane_of(an[j / 2][v], j & 1), lane_of(ad[j / 2][v], j & 1));
                 }
-                store_strip_global<T, VEC, VA>(og + j * SP + (long long)d * HW + (long long)hrow * W,
+                store_strip_global<T, VEC, VA>(og + j * SP + (long long)d * HW + hrow * RWZ,
                                                w0, W, ov);
             }
         }

@@ -113,8 +113,10 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
         if (vec && g.W == 64) return launch_fwd<T, KD, KH, KW, S, true, 16>(P, smem, BC, st);
         if (vec && g.W == 128) return launch_fwd<T, KD, KH, KW, S, true, 32>(P, smem, BC, st);
     }
-    if constexpr (KD > 1 && KH == 1) {
+    if constexpr (KD > 1 && KH == 1) {   // rows kernels: 256, 128 and 64 columns
         if (vec && g.W == 4 * S::NT) return launch_fwd<T, KD, KH, KW, S, true, S::NT>(P, smem, BC, st);
+        if (vec && S::NT == 64 && g.W == 128) return launch_fwd<T, KD, KH, KW, S, true, 32>(P, smem, BC, st);
+        if (vec && S::NT == 64 && g.W == 64) return launch_fwd<T, KD, KH, KW, S, true, 16>(P, smem, BC, st);
     }
     return vec ? launch_fwd<T, KD, KH, KW, S, true, 0>(P, smem, BC, st)
                : launch_fwd<T, KD, KH, KW, S, false, 0>(P, smem, BC, st);
@@ -229,17 +231,27 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     return true;
 }
 
-// 2-D images (5x5 or 3x3) of 65..256 columns are run as volumes of one-row planes (the same
-// memory and the same filter layout): returns the strips per row the kernels are built for, 0 for other shapes.
+// 2-D batches (5x5 or 3x3 kernels, up to 256 columns, at least 32 rows) are run as ONE volume per
+// group whose planes are the image rows and whose plane rows are the images of the batch (the
+// same memory and the same filter layout; kernel K x 1 x K, so images never mix).  A CTA takes
+// as many images as fill its threads (one image of 129..256 columns, four of 64, ...).  Returns
+// the CTA size class (strips of 4 per CTA), or 0 where the band kernels stay: a batch too small
+// to fill even the small CTA, or a band whose 32-bit offsets would overflow.
 inline int rows_class(const Geo& g) {
-    if (g.D != 1 || g.kD != 1 || g.kH != g.kW || (g.kH != 5 && g.kH != 3) || g.H < 32) return 0;
-    if (g.W > 128 && g.W <= 256) return 64;
-    if (g.W > 64 && g.W <= 128) return 32;
-    return 0;
+    if (g.D != 1 || g.kD != 1 || g.kH != g.kW || (g.kH != 5 && g.kH != 3) || g.H < 8) return 0;
+    const int NQ = (g.W + 3) / 4;
+    if (NQ > 64) return 0;
+    const int images = std::min(g.B, 64 / NQ);          // per CTA
+    const long long image = (long long)g.H * g.W;       // elements of one channel
+    if ((images * (long long)g.G + 1) * SCH * image >= (1LL << 31)) return 0;
+    const int strips = images * NQ;
+    return strips > 32 ? 64 : strips >= 24 ? 32 : 0;
 }
 inline Geo as_rows(const Geo& g) {
     Geo v = g;
-    v.D = g.H; v.H = 1; v.kD = g.kH; v.kH = 1; v.pD = g.pH; v.pH = 0;
+    v.B = 1; v.D = g.H; v.H = g.B;
+    v.kD = g.kH; v.kH = 1; v.pD = g.pH; v.pH = 0;
+    v.SP = (long long)v.D * v.H * v.W;
     return v;
 }
 
@@ -384,9 +396,13 @@ cudaError_t backward_shape(const Geo& g, const BwdPlan& p, const T* x, const T* 
         if (vec && g.W == 128)
             return backward_launch<T, KD, KH, KW, S, true, 32>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
     }
-    if constexpr (KD > 1 && KH == 1) {
+    if constexpr (KD > 1 && KH == 1) {   // rows kernels: 256, 128 and 64 columns
         if (vec && g.W == 4 * S::RatioNT)
             return backward_launch<T, KD, KH, KW, S, true, S::RatioNT>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+        if (vec && S::RatioNT == 64 && g.W == 128)
+            return backward_launch<T, KD, KH, KW, S, true, 32>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
+        if (vec && S::RatioNT == 64 && g.W == 64)
+            return backward_launch<T, KD, KH, KW, S, true, 16>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);
     }
     return vec ? backward_launch<T, KD, KH, KW, S, true, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st)
                : backward_launch<T, KD, KH, KW, S, false, 0>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, st);

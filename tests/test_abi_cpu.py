@@ -62,11 +62,17 @@ def test_query_accepts_and_rejects(lib):
     for spatial, want in [((256, 256), _lib.PATH_DEPTHWISE4_ROWS),    # the 2-D benchmark layer
                           ((128, 128), _lib.PATH_DEPTHWISE4_ROWS),
                           ((40, 65), _lib.PATH_DEPTHWISE4_ROWS),
-                          ((64, 64), _lib.PATH_DEPTHWISE4),           # too narrow for a row CTA
-                          ((31, 200), _lib.PATH_DEPTHWISE4),          # too few rows to march
+                          ((64, 64), _lib.PATH_DEPTHWISE4_ROWS),      # two images side by side per CTA
+                          ((6, 200), _lib.PATH_DEPTHWISE4),           # too few rows to march
                           ((64, 300), _lib.PATH_GENERIC)]:            # wider than a tile
         assert lib.ndc_query(_desc(spatial=spatial, **img), ctypes.byref(path)) == 0
         assert path.value == want, (spatial, path.value)
+    # a single narrow image cannot fill a row CTA: band kernels
+    assert lib.ndc_query(_desc(batch=1, spatial=(64, 64), **img), ctypes.byref(path)) == 0
+    assert path.value == _lib.PATH_DEPTHWISE4
+    assert lib.ndc_query(_desc(batch=16, groups=512, spatial=(32, 16), kernel_size=(5, 5)),
+                         ctypes.byref(path)) == 0
+    assert path.value == _lib.PATH_DEPTHWISE4_ROWS                    # sixteen images per CTA
     assert lib.ndc_query(_desc(groups=4, spatial=(128, 128), kernel_size=(3, 3)), ctypes.byref(path)) == 0
     assert path.value == _lib.PATH_DEPTHWISE4_ROWS
     assert lib.ndc_query(_desc(groups=4, spatial=(3, 40, 100), kernel_size=(1, 5, 5)),

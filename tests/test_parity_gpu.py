@@ -339,6 +339,11 @@ def test_tiled_kernels_match_generic_kernels_on_random_geometries(dev):
               (1, 1, (5, 5), (45, 255), False), (1, 1, (5, 5), (300, 128), True),
               (1, 3, (5, 5), (32, 65), True), (1, 1, (5, 5), (31, 200), True),
               (1, 2, (3, 3), (40, 100), True), (2, 1, (3, 3), (70, 131), False),
+              # several narrow images per row CTA: full, ragged and partly filled bands of images
+              (5, 2, (5, 5), (40, 64), True), (16, 1, (5, 5), (32, 16), True),
+              (7, 3, (5, 5), (50, 30), False), (9, 2, (3, 3), (45, 36), True),
+              (3, 1, (3, 3), (33, 16), True), (2, 2, (5, 5), (64, 64), True),
+              (16, 2, (5, 5), (8, 16), True), (4, 1, (5, 5), (7, 100), True), (6, 1, (3, 3), (9, 40), False),
               # a volume with a flat 1x5x5 kernel is not an image: stays on the band kernels
               (1, 2, (1, 5, 5), (3, 40, 100), True)]
     for B, C, ks, spatial, relu in cases:
