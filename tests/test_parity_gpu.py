@@ -215,6 +215,71 @@ def test_results_are_bitwise_reproducible(dev):
         assert torch.equal(a[k], b[k]), k
 
 
+def _seeded_case(dev, spatial, ks, B=2, C=4, seed=5):
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    x = torch.rand(B, C, *spatial, device=dev, generator=gen)
+    z = torch.randn(B, 4 * C, *spatial, device=dev, generator=gen) * 0.5 + 0.3
+    h = torch.rand(C, 4, *ks, device=dev, generator=gen) / float(np.prod(ks))
+    b = torch.randn(4 * C, device=dev, generator=gen) * 0.1
+    g = torch.randn(B, 4 * C, *spatial, device=dev, generator=gen)
+    return x, z, h, b, g
+
+
+def _fwd_bwd(x, z, h, b, g):
+    t = [v.detach().clone().requires_grad_(True) for v in (x, z, h, b)]
+    out = dcb.deconv_update(*t, groups=x.shape[1], m=1, sc=4, eps=1e-16, relu_input=True)
+    out.backward(g)
+    return [out.detach()] + [v.grad for v in t]
+
+
+@pytest.mark.parametrize("spatial,ks", [((12, 20, 40), (3, 3, 3)), ((40, 96), (5, 5))],
+                         ids=["volume", "images"])
+def test_work_goes_to_the_current_stream(dev, spatial, ks):
+    """The library launches on the stream it is handed (the caller's current stream): a run on
+    a side stream, ordered after its inputs by that stream alone, gives the same bits."""
+    case = _seeded_case(dev, spatial, ks)
+    ref = _fwd_bwd(*case)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        got = _fwd_bwd(*case)
+    side.synchronize()
+    for a, r in zip(got, ref):
+        assert torch.equal(a, r)
+
+
+def test_calls_can_be_captured_in_a_cuda_graph(dev):
+    """Forward and backward allocate nothing themselves and never synchronise, so a step can be
+    captured once and replayed on new data (as `bench_configs.py --graph` does)."""
+    x, z, h, b, g = _seeded_case(dev, (10, 12, 24), (3, 3, 3))
+    sx, sz = x.clone().requires_grad_(True), z.clone().requires_grad_(True)
+    sh, sb = h.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    cfg = dict(groups=x.shape[1], m=1, sc=4, eps=1e-16, relu_input=True)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):          # warm-up outside capture
+        dcb.deconv_update(sx, sz, sh, sb, **cfg).backward(g)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    for t in (sx, sz, sh, sb):
+        t.grad = None
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = dcb.deconv_update(sx, sz, sh, sb, **cfg)
+        out.backward(g)
+    for seed in (21, 22):
+        x2, z2, _, _, _ = _seeded_case(dev, (10, 12, 24), (3, 3, 3), seed=seed)
+        with torch.no_grad():
+            sx.copy_(x2)
+            sz.copy_(z2)
+        graph.replay()
+        torch.cuda.synchronize()
+        ref = _fwd_bwd(x2, z2, h, b, g)
+        for a, r in zip([out.detach(), sx.grad, sz.grad, sh.grad, sb.grad], ref):
+            assert torch.equal(a, r)
+
+
 def test_non_contiguous_input(dev):
     g = load_golden("layer_dw3d")
     mod = _layer(g, dev)
