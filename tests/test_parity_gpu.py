@@ -232,6 +232,26 @@ def _fwd_bwd(x, z, h, b, g):
     return [out.detach()] + [v.grad for v in t]
 
 
+@pytest.mark.parametrize("spatial,ks,B", [((40, 96), (5, 5), 2), ((24, 32), (5, 5), 5),
+                                          ((6, 6, 6), (3, 3, 3), 2)],
+                         ids=["images_rows", "images_rows_multi", "small_volume"])
+def test_partial_gradient_requests_on_other_kernel_families(dev, spatial, ks, B):
+    """The same subsets on the row-marching kernels (one and several images per CTA) and on the
+    narrow-CTA kernels of small volumes: the variants without filter-gradient sums run too."""
+    x, z, h, b, g = _seeded_case(dev, spatial, ks, B=B)
+    full = _fwd_bwd(x, z, h, b, g)
+    for mask in range(1, 16):
+        t = [v.detach().clone().requires_grad_(bool(mask >> i & 1)) for i, v in enumerate((x, z, h, b))]
+        out = dcb.deconv_update(*t, groups=x.shape[1], m=1, sc=4, eps=1e-16, relu_input=True)
+        out.backward(g)
+        assert torch.equal(out.detach(), full[0])
+        for i, v in enumerate(t):
+            if mask >> i & 1:
+                assert torch.equal(v.grad, full[1 + i]), (mask, i)
+            else:
+                assert v.grad is None
+
+
 @pytest.mark.parametrize("spatial,ks", [((12, 20, 40), (3, 3, 3)), ((40, 96), (5, 5))],
                          ids=["volume", "images"])
 def test_work_goes_to_the_current_stream(dev, spatial, ks):
@@ -355,7 +375,8 @@ def test_abi_status_codes_on_device(dev):
     (1, 32, (5, 5), (256, 256)),           # the 2-D benchmark geometry
     (2, 32, (3, 3, 3), (24, 40, 72)),      # width not a power of two, several bands
     (1, 8, (3, 3), (50, 132)),
-], ids=["cfg3", "cfg1", "odd3d", "odd2d"])
+    (6, 8, (5, 5), (40, 64)),              # four images per row CTA, a ragged last band
+], ids=["cfg3", "cfg1", "odd3d", "odd2d", "multi2d"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
 def test_tiled_kernels_match_generic_kernels_at_full_size(dev, shape, dtype):
     """At sizes the CPU oracle cannot finish quickly, the tiled depthwise kernels are checked
