@@ -2,6 +2,7 @@
 configurations (2-D forward, 3-D training step, large 3-D inference).
 
     python bench_configs.py --config triton      # layer: reference Triton path vs this library
+    python bench_configs.py --config 1           # 2-D layer forward: reference on the host cores vs this library
     python bench_configs.py --config 2           # full 2-D Deconver forward, fp32 and bf16
     python bench_configs.py --config 4 [--gpus N under torchrun]   # 3-D training step, bf16
     python bench_configs.py --config 5           # large 3-D inference, bf16, NDC share
@@ -146,6 +147,56 @@ def config_triton(dc, args):
         emit(config="triton", case=name, voxels=vox, forward_max_norm_diff=err, **res,
              speedup_fwd=res["reference_triton"]["fwd_ms"] / res["b200"]["fwd_ms"],
              speedup_fwd_bwd=res["reference_triton"]["fwd_bwd_ms"] / res["b200"]["fwd_bwd_ms"])
+
+
+def config_1(dc, args):
+    """Config 1 as BASELINE states it: one 2-D layer forward, fp32, X (1,32,256,256), seed 0,
+    K = |N(0,1)|/25 — the reference's own module on the host cores (its general PyTorch path)
+    next to this library on the GPU, same weights, with the difference between the two."""
+    import os
+
+    import deconver_b200
+    from deconver.deconvolution.deconv import Deconv as RefDeconv
+
+    kw = dict(channels=32, ratio=4, groups=-1, kernel_size=(5, 5))
+    torch.manual_seed(0)
+    ref = RefDeconv(**kw)
+    with torch.no_grad():
+        ref.init.h0.copy_(torch.randn(32, 4, 5, 5).abs() / 25)
+    x = torch.rand(1, 32, 256, 256)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    with torch.no_grad():
+        for _ in range(2):
+            y_cpu = ref(x)
+        import time
+        ts = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            ref(x)
+            ts.append((time.perf_counter() - t0) * 1e3)
+    cpu_ms = sorted(ts)[len(ts) // 2]
+    dev = torch.device("cuda", 0)
+    # fp32 config: the 1x1 projection (a library convolution) runs without TF32 here
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_tf32 = False
+    mine = deconver_b200.Deconv(**kw).to(dev)
+    mine.load_state_dict(ref.state_dict())
+    xd = x.to(dev)
+
+    def fwd():
+        with torch.no_grad():
+            mine(xd)
+
+    gpu_ms = timed(fwd)
+    with torch.no_grad():
+        y = mine(xd).cpu()
+    err = float((y.double() - y_cpu.double()).abs().max() / y_cpu.double().abs().max())
+    vox = 256 * 256
+    emit(config=1, voxels=vox, forward_max_norm_diff=err,
+         reference_cpu=dict(ms=cpu_ms, voxels_per_s=vox / cpu_ms * 1e3, cores=cores,
+                            path="reference Deconv, general PyTorch path, fp32"),
+         b200=dict(ms=gpu_ms, voxels_per_s=vox / gpu_ms * 1e3))
 
 
 def config_2(dc, args):
@@ -303,7 +354,7 @@ def config_5(dc, args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--config", required=True, choices=["triton", "2", "4", "5"])
+    ap.add_argument("--config", required=True, choices=["triton", "1", "2", "4", "5"])
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--chunk", type=int, default=4)
     ap.add_argument("--graph", action="store_true",
@@ -318,7 +369,7 @@ def main():
     if not torch.cuda.is_available():
         emit(config=args.config, unavailable="no CUDA device")
         return
-    {"triton": config_triton, "2": config_2, "4": config_4, "5": config_5}[args.config](dc, args)
+    {"triton": config_triton, "1": config_1, "2": config_2, "4": config_4, "5": config_5}[args.config](dc, args)
 
 
 if __name__ == "__main__":
