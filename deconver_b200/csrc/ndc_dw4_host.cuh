@@ -55,7 +55,7 @@ template <int KD, int KH, int KW, typename S = FwdShape<KD, KH, KW>>
 inline bool plan_fwd(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
     if ((long long)D * H * W >= (1LL << 29)) return false;  // 32-bit offsets inside a slab
-    if (W > 256) return false;
+    if (W > ((KD > 1 && KH == 1) ? 512 : 256)) return false;   // row kernels: up to 128 strips
     t.NQ = (W + 3) / 4;
     t.pitch = row_pitch(W);
     const int NS8 = (t.NQ + 1) / 2;
@@ -148,7 +148,7 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
                       int red_floats, size_t extra_bytes, size_t smem_target, int ctas_per_sm,
                       Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
-    if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
+    if ((long long)D * H * W >= (1LL << 29) || W > ((KD > 1 && KH == 1) ? 512 : 256)) return false;
     t.NQ = (W + 3) / 4;
     t.pitch = row_pitch(W);
     int TH = H;
@@ -170,7 +170,7 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
 template <int KD, int KH, int KW, int NT>
 inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
     constexpr int PH = KH / 2;
-    if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
+    if ((long long)D * H * W >= (1LL << 29) || W > ((KD > 1 && KH == 1) ? 512 : 256)) return false;
     t.NQ = (W + 3) / 4;
     t.pitch = row_pitch(W);
     const int NS8 = (t.NQ + 1) / 2;
@@ -240,12 +240,12 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
 inline int rows_class(const Geo& g) {
     if (g.D != 1 || g.kD != 1 || g.kH != g.kW || (g.kH != 5 && g.kH != 3) || g.H < 8) return 0;
     const int NQ = (g.W + 3) / 4;
-    if (NQ > 64) return 0;
-    const int images = std::min(g.B, 64 / NQ);          // per CTA
+    if (NQ > 128) return 0;
+    const int images = NQ > 64 ? 1 : std::min(g.B, 64 / NQ);   // per CTA
     const long long image = (long long)g.H * g.W;       // elements of one channel
     if ((images * (long long)g.G + 1) * SCH * image >= (1LL << 31)) return 0;
     const int strips = images * NQ;
-    return strips > 32 ? 64 : strips >= 24 ? 32 : 0;
+    return strips > 64 ? 128 : strips > 32 ? 64 : strips >= 24 ? 32 : 0;
 }
 inline Geo as_rows(const Geo& g) {
     Geo v = g;
@@ -260,6 +260,7 @@ template <int K>
 inline bool plan_bwd_image(const Geo& g, BwdPlan& p) {
     const int rc = rows_class(g);
     p.rows = rc;
+    if (rc == 128 && plan_bwd<K, 1, K, BwdRows<128>>(as_rows(g), p)) return true;
     if (rc == 64 && plan_bwd<K, 1, K, BwdRows<64>>(as_rows(g), p)) return true;
     if (rc == 32 && plan_bwd<K, 1, K, BwdRows<32>>(as_rows(g), p)) return true;
     p.rows = 0;
@@ -412,6 +413,8 @@ template <typename T, int K>
 cudaError_t backward_image(const Geo& g, const BwdPlan& p, const T* x, const T* z, const T* t1,
                            const float* h, const float* bias, const T* gout, T* gx, T* gz,
                            float* gh, float* gb, void* ws, int dtype, cudaStream_t st) {
+    if (p.rows == 128)
+        return backward_shape<T, K, 1, K, BwdRows<128>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
     if (p.rows == 64)
         return backward_shape<T, K, 1, K, BwdRows<64>>(as_rows(g), p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
     if (p.rows == 32)
@@ -447,6 +450,21 @@ inline int fwd_small_class(const Geo& g) {
     return 256;
 }
 
+// Forward plan of a K x K image batch: the row kernels of its class, else the band kernels.
+template <int K>
+inline bool plan_fwd_image(const Geo& g) {
+    Tiling t; size_t smem;
+    const int rc = rows_class(g);
+    if (rc) {
+        const Geo v = as_rows(g);
+        const long long BC = (long long)v.B * v.G;
+        if (rc == 128 && plan_fwd<K, 1, K, FwdRows<128>>(v.D, v.H, v.W, BC, t, smem)) return true;
+        if (rc == 64 && plan_fwd<K, 1, K, FwdRows<64>>(v.D, v.H, v.W, BC, t, smem)) return true;
+        if (rc == 32 && plan_fwd<K, 1, K, FwdRows<32>>(v.D, v.H, v.W, BC, t, smem)) return true;
+    }
+    return plan_fwd<1, K, K>(g.D, g.H, g.W, (long long)g.B * g.G, t, smem);
+}
+
 // Whether the tiled kernels take this geometry (pointer alignment only affects vector width).
 inline bool covers(const Geo& g) {
     if (g.m != 1 || g.sc != SCH || !shape_supported(g.kD, g.kH, g.kW)) return false;
@@ -455,8 +473,8 @@ inline bool covers(const Geo& g) {
     BwdPlan bp;
     if (!plan_bwd_any(g, bp)) return false;
     if (g.kD == 3) return plan_fwd<3, 3, 3>(g.D, g.H, g.W, BC, t, smem);
-    if (g.kH == 5) return plan_fwd<1, 5, 5>(g.D, g.H, g.W, BC, t, smem);
-    return plan_fwd<1, 3, 3>(g.D, g.H, g.W, BC, t, smem);
+    if (g.kH == 5) return plan_fwd_image<5>(g);
+    return plan_fwd_image<3>(g);
 }
 
 template <typename T, int K>
@@ -465,7 +483,9 @@ cudaError_t forward_image(const Geo& g, const T* x, const T* z, const float* h, 
     const int rc = rows_class(g);
     if (rc) {
         const Geo v = as_rows(g);
-        cudaError_t e = rc == 64
+        cudaError_t e = rc == 128
+            ? forward_shape<T, K, 1, K, FwdRows<128>>(v, x, z, h, bias, out, t1, dtype, st, handled)
+            : rc == 64
             ? forward_shape<T, K, 1, K, FwdRows<64>>(v, x, z, h, bias, out, t1, dtype, st, handled)
             : forward_shape<T, K, 1, K, FwdRows<32>>(v, x, z, h, bias, out, t1, dtype, st, handled);
         if (handled || e != cudaSuccess) return e;
@@ -511,6 +531,8 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
 #define NDC_DW4_BWD2D_INSTANCES(PREFIX, T)                                                    \
     PREFIX cudaError_t backward_shape<T, 1, 5, 5, BwdBands> NDC_DW4_BWD_ARGS(T);              \
     PREFIX cudaError_t backward_shape<T, 1, 3, 3, BwdBands> NDC_DW4_BWD_ARGS(T);              \
+    PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<128>> NDC_DW4_BWD_ARGS(T);          \
+    PREFIX cudaError_t backward_shape<T, 3, 1, 3, BwdRows<128>> NDC_DW4_BWD_ARGS(T);          \
     PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<64>> NDC_DW4_BWD_ARGS(T);           \
     PREFIX cudaError_t backward_shape<T, 5, 1, 5, BwdRows<32>> NDC_DW4_BWD_ARGS(T);           \
     PREFIX cudaError_t backward_shape<T, 3, 1, 3, BwdRows<64>> NDC_DW4_BWD_ARGS(T);           \

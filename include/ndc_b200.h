@@ -58,7 +58,7 @@ enum NdcPath {
     NDC_PATH_GENERIC = 0, /* any m, sc <= 16, any odd kernel with <= 343 taps                */
     NDC_PATH_DEPTHWISE4 = 1, /* m = 1, sc = 4, kernel 3x3x3, 1x5x5 or 1x3x3: tiled, fused    */
     NDC_PATH_DEPTHWISE4_ROWS = 2 /* the same kernels marching down the rows of 2-D images:
-                                    5x5 or 3x3, up to 256 columns, at least 8 rows, enough
+                                    5x5 or 3x3, up to 512 columns, at least 8 rows, enough
                                     images in the batch to fill a 32-thread CTA             */
 };
 

@@ -64,7 +64,8 @@ def test_query_accepts_and_rejects(lib):
                           ((40, 65), _lib.PATH_DEPTHWISE4_ROWS),
                           ((64, 64), _lib.PATH_DEPTHWISE4_ROWS),      # two images side by side per CTA
                           ((6, 200), _lib.PATH_DEPTHWISE4),           # too few rows to march
-                          ((64, 300), _lib.PATH_GENERIC)]:            # wider than a tile
+                          ((64, 300), _lib.PATH_DEPTHWISE4_ROWS),     # one wide image per 128-thread CTA
+                          ((64, 600), _lib.PATH_GENERIC)]:            # wider than a tile
         assert lib.ndc_query(_desc(spatial=spatial, **img), ctypes.byref(path)) == 0
         assert path.value == want, (spatial, path.value)
     # a single narrow image cannot fill a row CTA: band kernels

@@ -430,6 +430,8 @@ def test_tiled_kernels_match_generic_kernels_on_random_geometries(dev):
               (7, 3, (5, 5), (50, 30), False), (9, 2, (3, 3), (45, 36), True),
               (3, 1, (3, 3), (33, 16), True), (2, 2, (5, 5), (64, 64), True),
               (16, 2, (5, 5), (8, 16), True), (4, 1, (5, 5), (7, 100), True), (6, 1, (3, 3), (9, 40), False),
+              # images of 257..512 columns: one per 128-thread CTA
+              (1, 2, (5, 5), (20, 300), True), (2, 1, (5, 5), (33, 512), True), (1, 1, (3, 3), (40, 257), False),
               # a volume with a flat 1x5x5 kernel is not an image: stays on the band kernels
               (1, 2, (1, 5, 5), (3, 40, 100), True)]
     for B, C, ks, spatial, relu in cases:
