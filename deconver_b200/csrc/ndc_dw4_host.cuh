@@ -18,7 +18,7 @@ template <int KD, int KH, int KW> struct FwdShape;
 template <> struct FwdShape<3, 3, 3> { static constexpr int NT = 256, MAXZ = 5, MAXX = 1, MINB = 2; };
 template <> struct FwdShape<1, 5, 5> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
 template <> struct FwdShape<1, 3, 3> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
-// 2-D images of 65..256 columns run as volumes of one-row planes: rows become the marching axis,
+// 2-D image batches run as volumes of one-row planes: rows become the marching axis,
 // so nothing is recomputed between row bands and the loads of the next row overlap the work
 // on this one.  A CTA is as wide as one row has 4-voxel strips.
 template <int NT_> struct FwdRows { static constexpr int NT = NT_, MAXZ = 4, MAXX = 1, MINB = 384 / NT_; };
@@ -231,10 +231,10 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     return true;
 }
 
-// 2-D batches (5x5 or 3x3 kernels, up to 256 columns, at least 32 rows) are run as ONE volume per
+// 2-D batches (5x5 or 3x3 kernels, up to 512 columns, at least 8 rows) are run as ONE volume per
 // group whose planes are the image rows and whose plane rows are the images of the batch (the
 // same memory and the same filter layout; kernel K x 1 x K, so images never mix).  A CTA takes
-// as many images as fill its threads (one image of 129..256 columns, four of 64, ...).  Returns
+// as many images as fill its threads (one image of 129..512 columns, four of 64, ...).  Returns
 // the CTA size class (strips of 4 per CTA), or 0 where the band kernels stay: a batch too small
 // to fill even the small CTA, or a band whose 32-bit offsets would overflow.
 inline int rows_class(const Geo& g) {
