@@ -13,14 +13,25 @@ With N > 1 every rank works on its own batch of 2 (weak scaling, batch sharding)
 parameter gradients (dK, projection weight and bias) are averaged with one NCCL all-reduce
 inside the step.  `e2e` is the same step through the public `Deconv` module with pinned HOST
 input and upstream gradient, host<->device copies inside the timed region.
-`--impl reference` times the reference algorithm's PyTorch CPU path (the oracle port) on the
-host cores instead.
+
+`--impl reference` times the reference's own CPU implementation of the same layer
+(`ReferenceDeconv`, imported from an installation of the reference under `baseline/_ref`;
+the oracle's port of it when that directory is absent) on all host cores.
+
+Two sub-records ride along on the GPU arm when `baseline/_ref` is importable: `train_step`
+(the full 3-D network's training step, global batch 16 split over the ranks, at every N) and
+`triton` (the reference's own Triton kernels on the same GPU and layer, N = 1 only).
+
+`--profile-case` runs a few update calls on a small case and nothing else: the command the
+ncu summaries under `profiles/` were captured with.
 """
 
 import argparse
+import ctypes
 import json
 import math
 import os
+import re
 import statistics
 import sys
 import threading
@@ -29,6 +40,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+REF = os.path.join(ROOT, "baseline", "_ref")
 
 import torch
 
@@ -37,12 +49,19 @@ UNIT = "voxels/s"
 WORKLOAD = dict(channels=64, ratio=4, kernel_size=(3, 3, 3), batch=2, spatial=(64, 64, 64))
 WORKLOAD_NAME = ("single 3D NDC mixer layer fwd+bwd (dX, dK), fp32, X (2,64,64,64,64), "
                  "source 256 ch, K (256,1,3,3,3)")
-# measured on this pool's B200 with an FFMA-only kernel (profiles/fp32_fma_peak.md)
-FP32_FMA_PEAK_TFLOPS = 72.6
-# DRAM bytes (read + write) per ndc_bwd call: ncu capture at batch 1
-# (profiles/ndc_kernels_cfg3_b1_ncu_full.md: ratio 1445 MB + kconv 830 MB + gz 842 MB),
-# scaled by 2 to the bench workload's batch of 2 (traffic is proportional to voxels)
-BWD_DRAM_TRAFFIC_BYTES = 2 * (1445 + 830 + 842) * 1000 * 1000
+# DRAM traffic of one backward call, from an ncu capture at batch 1 (traffic is proportional to
+# voxels: every CTA works on its own slab); the capture's summary carries the figure
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "ndc_bwd_cfg3_b1_dram_traffic.txt")
+
+
+def config_of(world):
+    """The `config` object: the same for both arms, so their lines compare like with like."""
+    B = WORKLOAD["batch"]
+    return {
+        "workload": WORKLOAD_NAME, "per_gpu_batch": B, "global_batch": B * world,
+        "parallelism": f"batch-sharded x{world}" + (", NCCL grad all-reduce" if world > 1 else ""),
+        "l2": "inputs larger than L2 (x 134 MB, z/out/gout 537 MB each vs 126 MB L2)",
+    }
 
 
 def load_peaks():
@@ -52,6 +71,17 @@ def load_peaks():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def load_traffic(batch):
+    """(bytes per backward call at `batch`, provenance) from the tracked ncu summary, or
+    (None, reason)."""
+    try:
+        text = open(TRAFFIC_FILE).read()
+        per_b1 = int(re.search(r"^dram_bytes_per_call_batch1\s*=\s*(\d+)", text, re.M).group(1))
+        return per_b1 * batch, os.path.relpath(TRAFFIC_FILE, ROOT) + " (ncu, batch 1, scaled by batch)"
+    except Exception as exc:  # missing or unreadable summary: no figure rather than a stale one
+        return None, f"unavailable: {exc}"
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -112,77 +142,106 @@ class ClockSampler:
         }
 
 
-# ------------------------------------------------------------------------- CPU baseline
+# ------------------------------------------------------------------------- CPU arm
 
 
-def cpu_layer_step(batch, spatial, threads, seed=0):
-    """One forward+backward of the layer on the CPU with the oracle's PyTorch port of the
-    reference's eager path.  Returns seconds."""
-    from oracle import ndc_oracle
+class CpuLayer:
+    """The layer's forward + backward on the host cores: the reference's own `ReferenceDeconv`
+    when an installation of the reference is present, else the oracle's port of the same
+    eager path."""
 
-    torch.set_num_threads(threads)
-    C, r, ks = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"]
-    gen = torch.Generator().manual_seed(seed)
-    x = torch.rand(batch, C, *spatial, generator=gen).requires_grad_(True)
-    w = (torch.randn(C * r, C, 1, generator=gen) / C ** 0.5).requires_grad_(True)
-    b = torch.zeros(C * r).requires_grad_(True)
-    h0 = (torch.randn(C, r, *ks, generator=gen).abs() / 27).requires_grad_(True)
-    g = torch.randn(batch, C * r, *spatial, generator=gen)
-    t0 = time.perf_counter()
-    y = ndc_oracle.ndc_layer(x, w, b, h0, groups=C)
-    y.backward(g)
-    return time.perf_counter() - t0
+    def __init__(self):
+        self.threads = os.cpu_count() or 1
+        torch.set_num_threads(self.threads)
+        C, r, ks = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"]
+        self.mod = None
+        if os.path.isdir(os.path.join(REF, "deconver")):
+            try:
+                if REF not in sys.path:
+                    sys.path.insert(0, REF)
+                from deconver.deconvolution.reference import ReferenceDeconv
+                torch.manual_seed(0)
+                self.mod = ReferenceDeconv(channels=C, ratio=r, groups=-1, kernel_size=ks)
+                with torch.no_grad():
+                    self.mod.init.h0.copy_(torch.randn(C, r, *ks).abs() / 27)
+            except Exception as exc:
+                print(f"bench.py: reference installation not importable ({exc}); "
+                      "timing the oracle port", file=sys.stderr)
+                self.mod = None
+        self.kind = "reference" if self.mod is not None else "port"
+        self.what = ("reference ReferenceDeconv (general PyTorch path)" if self.mod is not None
+                     else "oracle port of the reference's general PyTorch path")
+
+    def step(self, batch, spatial, seed=0):
+        """One forward+backward; returns seconds."""
+        C, r, ks = WORKLOAD["channels"], WORKLOAD["ratio"], WORKLOAD["kernel_size"]
+        gen = torch.Generator().manual_seed(seed)
+        x = torch.rand(batch, C, *spatial, generator=gen).requires_grad_(True)
+        g = torch.randn(batch, C * r, *spatial, generator=gen)
+        if self.mod is not None:
+            self.mod.zero_grad(set_to_none=True)
+            t0 = time.perf_counter()
+            self.mod(x).backward(g)
+            return time.perf_counter() - t0
+        from oracle import ndc_oracle
+        w = (torch.randn(C * r, C, 1, generator=gen) / C ** 0.5).requires_grad_(True)
+        b = torch.zeros(C * r).requires_grad_(True)
+        h0 = (torch.randn(C, r, *ks, generator=gen).abs() / 27).requires_grad_(True)
+        t0 = time.perf_counter()
+        ndc_oracle.ndc_layer(x, w, b, h0, groups=C).backward(g)
+        return time.perf_counter() - t0
+
+    def sample_for(self, budget_s):
+        """Largest sample of the workload (whole, or a depth slab of one sample) whose step is
+        estimated to fit `budget_s`: (batch, spatial)."""
+        self.step(1, (4, 16, 16))          # thread-pool warm-up
+        per_voxel = self.step(1, (8, 64, 64)) / (8 * 64 * 64)
+        B, S = WORKLOAD["batch"], WORKLOAD["spatial"]
+        if per_voxel * B * S[0] * S[1] * S[2] <= budget_s:
+            return B, S
+        depth = int(max(4, min(S[0], budget_s / (per_voxel * S[1] * S[2]))))
+        return 1, (depth, S[1], S[2])
 
 
 def cpu_baseline(budget_s=25.0):
-    """Bounded CPU sample: the workload's volume cut to a depth slab so it fits the budget."""
-    threads = os.cpu_count() or 1
-    cpu_layer_step(1, (4, 16, 16), threads)  # thread-pool warm-up
-    probe_shape = (8, 64, 64)
-    t_probe = cpu_layer_step(1, probe_shape, threads)
-    per_voxel = t_probe / (8 * 64 * 64)
-    depth = int(max(8, min(64, budget_s / (per_voxel * 64 * 64))))
-    batch = 2 if per_voxel * 2 * 64 ** 3 <= budget_s else 1
-    if batch == 2:
-        depth = 64
-    spatial = (depth, 64, 64)
-    t = cpu_layer_step(batch, spatial, threads)
-    vox = batch * depth * 64 * 64
+    """Bounded CPU sample for the GPU arm's line: one step."""
+    cpu = CpuLayer()
+    batch, spatial = cpu.sample_for(budget_s)
+    t = cpu.step(batch, spatial)
+    vox = batch * spatial[0] * spatial[1] * spatial[2]
     return {
-        "value": vox / t, "unit": UNIT, "cores": threads, "kind": "port",
-        "sample": f"1 fwd+bwd of the layer on X ({batch},64,{depth},64,64), fp32, "
-                  f"torch {torch.__version__} CPU, {t:.2f} s",
+        "value": vox / t, "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind,
+        "sample": f"1 fwd+bwd of the layer on X ({batch},64,{spatial[0]},64,64), fp32, "
+                  f"{cpu.what}, torch {torch.__version__} CPU, {t:.2f} s",
     }
 
 
 def run_reference(args):
-    """`--impl reference`: the reference algorithm's CPU path, timed on the host cores."""
+    """`--impl reference`: the reference's CPU implementation of the layer on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    threads = os.cpu_count() or 1
-    cpu_layer_step(1, (4, 16, 16), threads)
-    t_probe = cpu_layer_step(1, (8, 64, 64), threads)
-    per_voxel = t_probe / (8 * 64 * 64)
+    world = max(1, args.gpus)
+    cpu = CpuLayer()
     total_steps = args.steps + args.warmup
-    budget = 150.0 / max(total_steps, 1)
-    depth = int(max(4, min(64, budget / (per_voxel * 64 * 64))))
-    spatial = (depth, 64, 64)
+    batch, spatial = cpu.sample_for(240.0 / max(total_steps, 1))
     for _ in range(args.warmup):
-        cpu_layer_step(1, spatial, threads)
-    times = [cpu_layer_step(1, spatial, threads) for _ in range(args.steps)]
+        cpu.step(batch, spatial)
+    times = [cpu.step(batch, spatial) for _ in range(args.steps)]
     total = sum(times)
-    vox = depth * 64 * 64
+    vox = batch * spatial[0] * spatial[1] * spatial[2]
     value = vox * args.steps / total
-    sample = (f"{args.steps} fwd+bwd steps of the layer on X (1,64,{depth},64,64) "
-              f"(depth slab of the workload), fp32, PyTorch CPU, {threads} threads")
+    whole = (batch, tuple(spatial)) == (WORKLOAD["batch"], tuple(WORKLOAD["spatial"]))
+    sample = (f"{args.steps} fwd+bwd steps of the layer on X ({batch},64,{spatial[0]},64,64) "
+              f"({'the whole workload' if whole else 'a depth slab of the workload'}), fp32, "
+              f"{cpu.what}, {cpu.threads} threads")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * total / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD_NAME, "sample": sample},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+        "config": config_of(world),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cpu.threads, "kind": cpu.kind,
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -191,6 +250,65 @@ def run_reference(args):
 
 
 # ----------------------------------------------------------------------------- GPU arm
+
+
+def measure_fp32_fma_peak(lib, dev):
+    """TFLOP/s of register-only float32 multiply-add chains on this GPU, measured now with the
+    library's probe kernel (plain `fmaf` and packed `fma.rn.f32x2`; the better of the two)."""
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    out = torch.empty(sms * 4 * 256, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    best = {}
+    for packed in (0, 1):
+        n = ctypes.c_uint64(0)
+        iters = 4096
+        for _ in range(2):   # warm-up
+            st = lib.ndc_probe_fp32_fma(packed, iters, out.data_ptr(), out.numel(), ctypes.byref(n), stream)
+            if st != 0:
+                return None
+        times = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            lib.ndc_probe_fp32_fma(packed, iters, out.data_ptr(), out.numel(), ctypes.byref(n), stream)
+            b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b))
+        best["packed" if packed else "scalar"] = 2.0 * n.value / (min(times) * 1e-3) / 1e12
+    return best
+
+
+def sub_records(args, world, rank):
+    """`train_step` (every N) and `triton` (N = 1): measured through bench_configs.py's code
+    with the reference's own network around this library's layer."""
+    out = {}
+    if args.no_sub_records:
+        return out
+    try:
+        import bench_configs
+        dc = bench_configs.load_reference()
+    except Exception as exc:
+        dc, why = None, f"reference installation not importable: {exc}"
+    else:
+        why = "baseline/_ref (an installation of the reference) is not present"
+    if dc is None:
+        out["train_step"] = {"unavailable": why}
+        if world == 1:
+            out["triton"] = {"unavailable": why}
+        return out
+    try:
+        rec = bench_configs.train_step_record(dc, steps=8, graph=False)
+        rec["workload"] = ("full 3D Deconver training step (fwd+bwd+SGD), bf16, global batch 16 "
+                           "of 2x64^3 split over the ranks (strong scaling)")
+        out["train_step"] = rec
+    except Exception as exc:
+        out["train_step"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    if world == 1:
+        try:
+            out["triton"] = bench_configs.triton_record(dc, "cfg3")
+        except Exception as exc:
+            out["triton"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    return out
 
 
 def run_b200(args):
@@ -323,7 +441,12 @@ def run_b200(args):
     e2e_value = world * vox_per_step * e2e_steps / (float(te.item()) * 1e-3)
     h2d = x_host.numel() * 4 + g_host.numel() * 4
     d2h = y_host.numel() * 4 + gx_host.numel() * 4 + grads_host.numel() * 4
+    del x_dev, g_dev, x_host, g_host, y_host, gx_host
+    fma_peak = measure_fp32_fma_peak(lib, dev) if rank == 0 else None
+    del x, gout, layer, bucket
+    torch.cuda.empty_cache()
 
+    extra = sub_records(args, world, rank)   # collective: every rank takes part
     if rank != 0:
         return
 
@@ -338,50 +461,52 @@ def run_b200(args):
     bwd_flops = 2 * 8 * r * taps * C * vox_per_step
     fwd_flops = 2 * 3 * r * taps * C * vox_per_step
     achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9 if bwd_ms else None
+    fma_tflops = max(fma_peak.values()) if fma_peak else None
+    traffic, traffic_source = load_traffic(B)
+
+    def fma_frac(flops, ms):
+        return flops / (ms * 1e-3) / 1e12 / fma_tflops if (ms and fma_tflops) else None
+
     roofline = {
         "bound": "hbm", "kernel": "ndc_bwd (all launches of one backward call)",
         "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": achieved / peak if achieved else None, "peak_kind": peak_kind,
-        "traffic": BWD_DRAM_TRAFFIC_BYTES,
+        "traffic": traffic, "traffic_source": traffic_source,
         "algorithmic_bytes": bwd_bytes, "ms": bwd_ms,
         "fp32_fma": {
             "achieved_tflops": bwd_flops / (bwd_ms * 1e-3) / 1e12 if bwd_ms else None,
-            "peak_tflops": FP32_FMA_PEAK_TFLOPS,
-            "frac": bwd_flops / (bwd_ms * 1e-3) / 1e12 / FP32_FMA_PEAK_TFLOPS if bwd_ms else None,
+            "peak_tflops": fma_tflops, "peak_kind": "measured by this run (ndc_probe_fp32_fma)",
+            "peak_detail": fma_peak, "frac": fma_frac(bwd_flops, bwd_ms),
         },
         "fwd": {
             "ms": fwd_ms, "algorithmic_bytes": fwd_bytes,
             "achieved": fwd_bytes / (fwd_ms * 1e-3) / 1e9 if fwd_ms else None,
             "frac": fwd_bytes / (fwd_ms * 1e-3) / 1e9 / peak if fwd_ms else None,
-            "fp32_fma_frac": fwd_flops / (fwd_ms * 1e-3) / 1e12 / FP32_FMA_PEAK_TFLOPS
-            if fwd_ms else None,
+            "fp32_fma_frac": fma_frac(fwd_flops, fwd_ms),
         },
         "fwd_bwd_frac": (fwd_bytes + bwd_bytes) / ((fwd_ms + bwd_ms) * 1e-3) / 1e9 / peak
         if fwd_ms and bwd_ms else None,
+        "fwd_bwd_fp32_fma_frac": fma_frac(fwd_flops + bwd_flops, (fwd_ms or 0) + (bwd_ms or 0))
+        if fwd_ms and bwd_ms else None,
     }
 
-    path = _lib.load().ndc_query  # which kernel family ran
-    import ctypes
     pth = ctypes.c_int32(-1)
-    path(_lib.make_desc(B, C, 1, r, S, ks, 1e-16, True, _lib.NDC_F32), ctypes.byref(pth))
+    lib.ndc_query(_lib.make_desc(B, C, 1, r, S, ks, 1e-16, True, _lib.NDC_F32), ctypes.byref(pth))
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {
-            "workload": WORKLOAD_NAME, "per_gpu_batch": B, "global_batch": B * world,
-            "parallelism": f"batch-sharded x{world}" + (", NCCL grad all-reduce" if world > 1 else ""),
-            "l2": "inputs larger than L2 (x 134 MB, z/out/gout 537 MB each vs 126 MB L2)",
-            "kernel_path": {0: "generic", 1: "depthwise4", 2: "depthwise4_rows"}.get(pth.value, "?"),
-        },
+        "config": config_of(world),
+        "kernel_path": {0: "generic", 1: "depthwise4", 2: "depthwise4_rows"}.get(pth.value, "?"),
         "roofline": roofline,
         "clocks": clocks.summary(),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps},
         "gpu_launches": int(launches),
     }
+    line.update(extra)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
     print(json.dumps(line), flush=True)
@@ -431,6 +556,8 @@ def main():
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true",
                     help="skip the CPU-baseline leg (profiling runs)")
+    ap.add_argument("--no-sub-records", action="store_true",
+                    help="skip the train_step and triton sub-records")
     ap.add_argument("--profile-case", action="store_true",
                     help="run only a few update calls at --batch (for an ncu capture)")
     ap.add_argument("--batch", type=int, default=1, help="batch of --profile-case")

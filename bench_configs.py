@@ -108,45 +108,54 @@ def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, dept
 # ------------------------------------------------------------------------------- configs
 
 
-def config_triton(dc, args):
-    """Layer-level: reference `Deconv` (its Triton fast path) vs this library, same weights."""
+TRITON_CASES = {
+    "cfg3": ("cfg3 3D layer", dict(channels=64, ratio=4, groups=-1, kernel_size=(3, 3, 3)), (2, 64, 64, 64, 64)),
+    "cfg1": ("cfg1 2D layer", dict(channels=32, ratio=4, groups=-1, kernel_size=(5, 5)), (1, 32, 256, 256)),
+}
+
+
+def triton_record(dc, case="cfg3", dev=None):
+    """Layer-level: reference `Deconv` (its Triton fast path) vs this library, same weights, on
+    one GPU.  Returns a dict (times in ms, CUDA events, median of 7 after 2 warm-ups)."""
     import deconver_b200
     from deconver.deconvolution.deconv import Deconv as RefDeconv
 
-    dev = torch.device("cuda", 0)
-    for name, kw, shape in (
-        ("cfg3 3D layer", dict(channels=64, ratio=4, groups=-1, kernel_size=(3, 3, 3)), (2, 64, 64, 64, 64)),
-        ("cfg1 2D layer", dict(channels=32, ratio=4, groups=-1, kernel_size=(5, 5)), (1, 32, 256, 256)),
-    ):
-        torch.manual_seed(0)
-        ref = RefDeconv(**kw).to(dev)
-        mine = deconver_b200.Deconv(**kw).to(dev)
-        mine.load_state_dict(ref.state_dict())
-        x = torch.rand(*shape, device=dev)
-        g = torch.randn(shape[0], 4 * shape[1], *shape[2:], device=dev)
-        vox = shape[0]
-        for s in shape[2:]:
-            vox *= s
-        res = {}
-        for tag, mod in (("reference_triton", ref), ("b200", mine)):
-            fast = bool(mod.fast_path_applicable(x))
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    name, kw, shape = TRITON_CASES[case]
+    torch.manual_seed(0)
+    ref = RefDeconv(**kw).to(dev)
+    mine = deconver_b200.Deconv(**kw).to(dev)
+    mine.load_state_dict(ref.state_dict())
+    x = torch.rand(*shape, device=dev)
+    g = torch.randn(shape[0], 4 * shape[1], *shape[2:], device=dev)
+    vox = shape[0]
+    for s in shape[2:]:
+        vox *= s
+    res = {}
+    for tag, mod in (("reference_triton", ref), ("b200", mine)):
+        fast = bool(mod.fast_path_applicable(x))
 
-            def fwd():
-                with torch.no_grad():
-                    mod(x)
+        def fwd():
+            with torch.no_grad():
+                mod(x)
 
-            def fwdbwd():
-                xi = x.detach().requires_grad_(True)
-                mod.zero_grad(set_to_none=True)
-                mod(xi).backward(g)
+        def fwdbwd():
+            xi = x.detach().requires_grad_(True)
+            mod.zero_grad(set_to_none=True)
+            mod(xi).backward(g)
 
-            res[tag] = dict(fast_path=fast, fwd_ms=timed(fwd), fwd_bwd_ms=timed(fwdbwd))
-        with torch.no_grad():
-            a, b = ref(x), mine(x)
-        err = float((a.double() - b.double()).abs().max() / b.double().abs().max())
-        emit(config="triton", case=name, voxels=vox, forward_max_norm_diff=err, **res,
-             speedup_fwd=res["reference_triton"]["fwd_ms"] / res["b200"]["fwd_ms"],
-             speedup_fwd_bwd=res["reference_triton"]["fwd_bwd_ms"] / res["b200"]["fwd_bwd_ms"])
+        res[tag] = dict(fast_path=fast, fwd_ms=timed(fwd), fwd_bwd_ms=timed(fwdbwd))
+    with torch.no_grad():
+        a, b = ref(x), mine(x)
+    err = float((a.double() - b.double()).abs().max() / b.double().abs().max())
+    return dict(case=name, voxels=vox, forward_max_norm_diff=err, **res,
+                speedup_fwd=res["reference_triton"]["fwd_ms"] / res["b200"]["fwd_ms"],
+                speedup_fwd_bwd=res["reference_triton"]["fwd_bwd_ms"] / res["b200"]["fwd_bwd_ms"])
+
+
+def config_triton(dc, args):
+    for case in TRITON_CASES:
+        emit(config="triton", **triton_record(dc, case, torch.device("cuda", 0)))
 
 
 def config_1(dc, args):
@@ -228,10 +237,11 @@ def config_2(dc, args):
             del model
 
 
-def config_4(dc, args):
+def train_step_record(dc, steps=10, graph=False, per_gpu_batch=0):
     """Full 3-D training step (fwd + bwd + SGD), bf16, global batch 16 of 2 x 64^3, batch
-    sharded, NCCL all-reduce of all parameter gradients.  The reference has no loss or
-    optimizer: BCE-with-logits and plain SGD stand in."""
+    sharded over the ranks of the current process group (strong scaling), NCCL all-reduce of
+    all parameter gradients.  The reference has no loss or optimizer: BCE-with-logits and plain
+    SGD stand in.  Returns a dict; ms_per_step is the maximum over ranks (CUDA events)."""
     import torch.distributed as dist
     from deconver_b200.distributed import GradBucket, init_from_env, shard_batch
 
@@ -242,7 +252,7 @@ def config_4(dc, args):
     model = model.to(device=dev, dtype=torch.bfloat16).train()
     sl = shard_batch(16, rank, world)
     gen = torch.Generator(device=dev).manual_seed(100 + rank)
-    nb = args.per_gpu_batch or (sl.stop - sl.start)
+    nb = per_gpu_batch or (sl.stop - sl.start)
     x = torch.rand(nb, 2, 64, 64, 64, device=dev, generator=gen).to(torch.bfloat16)
     y = (torch.rand(nb, 1, 64, 64, 64, device=dev, generator=gen) < 0.05).to(torch.bfloat16)
     params = [p for p in model.parameters() if p.requires_grad]
@@ -266,7 +276,7 @@ def config_4(dc, args):
         return loss
 
     step = eager_step
-    if args.graph:
+    if graph:
         # forward + backward + gradient gather replayed as one CUDA graph (x, y and the
         # gradients keep their addresses); the all-reduce and the optimizer stay outside
         side = torch.cuda.Stream()
@@ -278,12 +288,13 @@ def config_4(dc, args):
         torch.cuda.synchronize()
         for p in params:
             p.grad = None
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        cuda_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cuda_graph):
             static_loss = fwd_bwd()
             bucket.gather()
+
         def step():
-            graph.replay()
+            cuda_graph.replay()
             bucket.allreduce_mean(gather=False)
             opt.step()
             return static_loss
@@ -295,21 +306,28 @@ def config_4(dc, args):
         dist.barrier()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         loss = step()
     b.record()
     torch.cuda.synchronize()
     t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / args.steps
+    ms = float(t.item()) / steps
     clock.reset()
     with torch.no_grad():
         model(x)
     ndc_fwd = clock.total_ms()
-    emit(config=4, n_gpus=world, global_batch=16, per_gpu_batch=nb, dtype="bfloat16",
-         cuda_graph=bool(args.graph), ms_per_step=ms, voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss),
-         ndc_forward_ms_per_rank=ndc_fwd, params=sum(p.numel() for p in params))
+    return dict(n_gpus=world, global_batch=16, per_gpu_batch=nb, dtype="bfloat16",
+                cuda_graph=bool(graph), steps=steps, ms_per_step=ms,
+                voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss),
+                ndc_forward_ms_per_rank=ndc_fwd, params=sum(p.numel() for p in params))
+
+
+def config_4(dc, args):
+    import torch.distributed as dist
+
+    emit(config=4, **train_step_record(dc, args.steps, args.graph, args.per_gpu_batch))
     if dist.is_initialized():
         dist.destroy_process_group()
 

@@ -19,6 +19,7 @@ FLAG_FORCE_GENERIC = 1
 SYMBOLS = (
     "ndc_version", "ndc_last_error", "ndc_status_string", "ndc_launch_count", "ndc_query",
     "ndc_fwd", "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_bwd_static", "ndc_gconv",
+    "ndc_probe_fp32_fma",
 )
 
 
@@ -74,6 +75,9 @@ def load():
     lib.ndc_bwd_static.argtypes = [dp, vp, vp, vp, fp, fp, vp, vp, vp, fp, fp, vp]
     lib.ndc_gconv.restype = ctypes.c_int
     lib.ndc_gconv.argtypes = [dp, vp, fp, fp, ctypes.c_int32, vp, vp]
+    lib.ndc_probe_fp32_fma.restype = ctypes.c_int
+    lib.ndc_probe_fp32_fma.argtypes = [ctypes.c_int32, ctypes.c_int32, fp, ctypes.c_size_t,
+                                       ctypes.POINTER(ctypes.c_uint64), vp]
     _lib = lib
     return lib
 

@@ -76,6 +76,53 @@ int path_of(const NdcDesc* d) {
 
 }  // namespace
 
+// ---- measurement aid: register-only chains of fused multiply-adds ------------------------
+namespace {
+
+template <bool PACKED>
+__global__ void __launch_bounds__(256) fma_chain_kernel(float* out, int iters, float a, float b) {
+    constexpr int ILP = 8;   // independent chains per thread
+    if (PACKED) {
+        unsigned long long acc[ILP], av, bv;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(av) : "f"(a));
+        asm("mov.b64 %0, {%1, %1};" : "=l"(bv) : "f"(b));
+#pragma unroll
+        for (int i = 0; i < ILP; ++i) {
+            const float v = threadIdx.x * 0.001f + i;
+            asm("mov.b64 %0, {%1, %1};" : "=l"(acc[i]) : "f"(v));
+        }
+        for (int it = 0; it < iters; ++it)
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int i = 0; i < ILP; ++i)
+                    asm volatile("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(acc[i]) : "l"(av), "l"(bv));
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ILP; ++i) {
+            float lo, hi;
+            asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[i]));
+            s += lo + hi;
+        }
+        out[blockIdx.x * blockDim.x + threadIdx.x] = s;
+    } else {
+        float acc[ILP];
+#pragma unroll
+        for (int i = 0; i < ILP; ++i) acc[i] = threadIdx.x * 0.001f + i;
+        for (int it = 0; it < iters; ++it)
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int i = 0; i < ILP; ++i) acc[i] = fmaf(acc[i], a, b);
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ILP; ++i) s += acc[i];
+        out[blockIdx.x * blockDim.x + threadIdx.x] = s;
+    }
+}
+
+}  // namespace
+
 extern "C" {
 
 int ndc_version(void) { return NDC_B200_VERSION; }
@@ -239,6 +286,30 @@ int ndc_bwd_static(const NdcDesc* desc, const void* x, const void* z, const void
     }
     return ndc_bwd(desc, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws,
                    (size_t)NDC_STATIC_WORKSPACE_BYTES, stream);
+}
+
+int ndc_probe_fp32_fma(int32_t packed, int32_t iters, float* out, size_t out_elems,
+                       uint64_t* fma_count, void* stream) {
+    if (iters <= 0) return fail(NDC_ERR_INVALID, "ndc_probe_fp32_fma: iters must be positive");
+    NDC_TRY(check_ptr(out, "out", NDC_F32));
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "ndc_probe_fp32_fma: device query");
+    const int threads = 256, blocks = sms * 4;
+    if (out_elems < (size_t)threads * blocks)
+        return fail(NDC_ERR_WORKSPACE, "ndc_probe_fp32_fma: out must hold %d floats, %zu given",
+                    threads * blocks, out_elems);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (packed) fma_chain_kernel<true><<<blocks, threads, 0, st>>>(out, iters, 0.999f, 0.001f);
+    else fma_chain_kernel<false><<<blocks, threads, 0, st>>>(out, iters, 0.999f, 0.001f);
+    ndc::launched();
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "ndc_probe_fp32_fma launch");
+    // per thread: iters x 8 rounds x 8 chains, two lanes per packed instruction
+    if (fma_count)
+        *fma_count = (uint64_t)threads * blocks * (uint64_t)iters * 64u * (packed ? 2u : 1u);
+    return NDC_OK;
 }
 
 int ndc_gconv(const NdcDesc* desc, const void* in, const float* h, const float* bias,

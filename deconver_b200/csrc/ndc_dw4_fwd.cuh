@@ -312,8 +312,10 @@ __global__ void __launch_bounds__(NT, MINB) fwd_kernel(const FwdParams P) {
             }
             if (row < 0) return;
             const int w0 = VK * strip + VA * cpair;
+            // the ring holds t1 as it is stored (rounded to the storage type), so the
+            // denominator here is the one backward recomputes from the saved t1
 #pragma unroll
-            for (int v = 0; v < VA; ++v) if (w0 + v >= W) tv[v] = 0.0f;
+            for (int v = 0; v < VA; ++v) tv[v] = (w0 + v >= W) ? 0.0f : to_f32(from_f32<T>(tv[v]));
             store_strip<VA, PW, false>(t1ring + slot_of(qdone) * lay.plane_t + row * pitch, w0, tv);
             const int h = h0 - PH + row;
             if (qdone >= d0 && qdone < d1 && row >= PH && row < PH + TH)

@@ -9,7 +9,20 @@
 namespace ndc {
 namespace dw4 {
 
-constexpr int kNumSMs = 148;
+// Multiprocessors of the current device (148 on B200), asked once per process; 148 where no
+// device answers (planning on a host without a GPU).
+inline int num_sms() {
+    static const int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) {
+            (void)cudaGetLastError();   // planning must not leave an error behind
+            v = 148;
+        }
+        return v;
+    }();
+    return n;
+}
 constexpr size_t kSmemTwoPerSM = 112 * 1024;   // lets two CTAs share an SM
 constexpr size_t kSmemMax = 227 * 1024;
 
@@ -41,7 +54,7 @@ inline void plan_depth(int KD, int D, long long ctas_per_chunk, int waves, Tilin
     } else {
         const int PD = KD / 2;
         const long long per = std::max(1LL, ctas_per_chunk);
-        const long long one_wave = (long long)ctas_per_sm * kNumSMs;
+        const long long one_wave = (long long)ctas_per_sm * num_sms();
         long long ndc = std::min(waves * one_wave / per, (long long)std::max(1, D / (16 * PD)));
         if (ndc * per < one_wave)
             ndc = std::min((one_wave + per - 1) / per, (long long)std::max(1, D / (4 * PD)));
@@ -310,6 +323,8 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
     float* pa = (float*)((char*)ws + p.off_pa);
     float* pa2 = (float*)((char*)ws + p.off_pa2);
     float* pb = (float*)((char*)ws + p.off_pb);
+    if (p.n_ratio > 0x7fffffffLL || p.n_kconv > 0x7fffffffLL || p.n_gz > 0x7fffffffLL)
+        return cudaErrorInvalidConfiguration;
     {
         RatioParams P;
         P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;

@@ -114,13 +114,14 @@ def _f32(t: Optional[Tensor]) -> Optional[Tensor]:
     return None if t is None else t.detach().to(torch.float32).contiguous()
 
 
-def _desc(x: Tensor, groups: int, m: int, sc: int, ks, eps: float, relu_input: bool):
+def _desc(x: Tensor, groups: int, m: int, sc: int, ks, eps: float, relu_input: bool,
+          flags: Optional[int] = None):
     if x.dtype not in _DTYPES:
         raise NotImplementedError(
             f"deconver_b200: dtype {x.dtype} is not supported (float32 and bfloat16 are)"
         )
     return _lib.make_desc(x.shape[0], groups, m, sc, x.shape[2:], ks, eps, relu_input,
-                          _DTYPES[x.dtype], _flags)
+                          _DTYPES[x.dtype], _flags if flags is None else flags)
 
 
 def _check_shapes(x, z, h, bias, groups, m, sc):
@@ -149,7 +150,8 @@ class DeconvUpdate(torch.autograd.Function):
         x = x.contiguous()
         z = z.contiguous()
         ks = tuple(h.shape[2:])
-        desc = _desc(x, groups, m, sc, ks, eps, relu_input)
+        flags = _flags   # read once: backward runs later, on an autograd thread
+        desc = _desc(x, groups, m, sc, ks, eps, relu_input, flags)
         hf, bf = _f32(h), _f32(bias)
         out = torch.empty_like(z)
         t1 = torch.empty_like(x)
@@ -159,7 +161,7 @@ class DeconvUpdate(torch.autograd.Function):
                 with timing.span("ndc_fwd"):
                     _lib.check(_lib.load().ndc_fwd(desc, _ptr(x), _ptr(z), _ptr(hf), _ptr(bf),
                                                    _ptr(out), _ptr(t1), stream))
-        ctx.cfg = (groups, m, sc, eps, relu_input)
+        ctx.cfg = (groups, m, sc, eps, relu_input, flags)
         ctx.save_for_backward(x, z, t1, h, bias)
         return out
 
@@ -173,7 +175,7 @@ class DeconvUpdate(torch.autograd.Function):
                 "double backward through the fused Deconv update is not supported"
             )
         x, z, t1, h, bias = ctx.saved_tensors
-        groups, m, sc, eps, relu_input = ctx.cfg
+        groups, m, sc, eps, relu_input, flags = ctx.cfg
         need_x, need_z, need_h, need_b = ctx.needs_input_grad[:4]
         need_b = need_b and bias is not None
         if not (need_x or need_z or need_h or need_b):
@@ -183,7 +185,7 @@ class DeconvUpdate(torch.autograd.Function):
         if gout.dtype != x.dtype:
             gout = gout.to(x.dtype)
         ks = tuple(h.shape[2:])
-        desc = _desc(x, groups, m, sc, ks, eps, relu_input)
+        desc = _desc(x, groups, m, sc, ks, eps, relu_input, flags)
         hf, bf = _f32(h), _f32(bias)
         gx = torch.empty_like(x) if need_x else None
         gz = torch.empty_like(z) if (need_z or need_b) else None

@@ -137,8 +137,10 @@ int ndc_bwd(const NdcDesc *desc, const void *x, const void *z, const void *t1, c
             void *workspace, size_t workspace_bytes, void *stream);
 
 /*
- * Size of the library-owned scratch array used by ndc_bwd_static.  Every GPU on which this
- * library is loaded holds these bytes from load until the process exits.
+ * Size of the library-owned scratch array used by ndc_bwd_static.  Every GPU that uses this
+ * library holds these bytes until the process exits.  When they are reserved depends on the
+ * CUDA module-loading mode: with lazy loading (the default) it can be as late as the first
+ * ndc_bwd_static call on that device, so make that call at start-up, while memory is there.
  */
 #define NDC_STATIC_WORKSPACE_BYTES (16u * 1024u * 1024u)
 
@@ -153,11 +155,14 @@ int ndc_bwd(const NdcDesc *desc, const void *x, const void *z, const void *t1, c
  *
  *  - Same arguments and results as ndc_bwd, minus the workspace.  No cudaMalloc, cudaFree or
  *    any other allocating call is made.
- *  - Limit: the geometry must need at most NDC_STATIC_WORKSPACE_BYTES of scratch
- *    (ndc_bwd_workspace_bytes tells); larger ones are refused with NDC_ERR_WORKSPACE and a
- *    message naming both numbers.  Roughly: batch * groups * 9 * D*H*W * 4 bytes must fit.
+ *  - Limit: the geometry must need at most NDC_STATIC_WORKSPACE_BYTES of scratch; ask
+ *    ndc_bwd_workspace_bytes for the exact figure of a geometry (it depends on the kernel
+ *    family and its tiling, not only on the tensor sizes).  Larger ones are refused with
+ *    NDC_ERR_WORKSPACE and a message naming both numbers.
  *  - The first call on each device looks up the array's device address (once per device,
- *    with that device current).  Make that first call before starting any stream capture.
+ *    with that device current) and may be the moment the driver reserves the array.  Make
+ *    that first call at start-up: before any stream capture, and before device memory is
+ *    handed out to pools that could leave too little for it.
  *  - All calls on a device share the one array and it keeps whatever the last call left in
  *    it.  Nothing in it needs to start at zero: every value is written before it is read.
  *    Two calls whose kernels can overlap on the GPU (different streams, or different host
@@ -166,6 +171,18 @@ int ndc_bwd(const NdcDesc *desc, const void *x, const void *z, const void *t1, c
 int ndc_bwd_static(const NdcDesc *desc, const void *x, const void *z, const void *t1,
                    const float *h, const float *bias, const void *gout, void *gx, void *gz,
                    float *gh, float *gb, void *stream);
+
+/*
+ * Measurement aid; no counterpart in the reference project.  Launches one kernel of
+ * register-only fused multiply-add chains (4 blocks of 256 threads per multiprocessor, 8
+ * independent chains per thread, iters x 64 instructions per thread) on `stream`: plain
+ * `fmaf` (packed = 0) or the two-lane `fma.rn.f32x2` (packed = 1).  `out` receives one float
+ * per thread (out_elems >= 1024 x the device's multiprocessor count).  *fma_count is set to
+ * the number of scalar multiply-adds the launch performs; timing it (CUDA events on the
+ * same stream) gives the float32 multiply-add peak the NDC kernels are measured against.
+ */
+int ndc_probe_fp32_fma(int32_t packed, int32_t iters, float *out, size_t out_elems,
+                       uint64_t *fma_count, void *stream);
 
 /*
  * Grouped convolution K (adjoint = 0: groups*sc -> groups*m channels) or its adjoint A

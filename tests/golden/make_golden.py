@@ -22,6 +22,17 @@ Two kinds of fixture:
 * `cfg1_digest.npz` - the 2-D benchmark geometry (1,32,256,256), k=5x5, ratio 4: parameters
   plus a strided subsample and norms of the forward result (the full tensors are too large
   to commit; `x` is regenerated from its seed at test time).
+* `cfg3_digest.npz` - the 3-D benchmark geometry, forward and backward: X (2,64,64,64,64),
+  k=3x3x3, ratio 4, upstream gradient N(0,1); parameters, strided subsamples of the output
+  and of the input gradient, and the full parameter gradients, from a float64 run (`x` and
+  the upstream gradient are regenerated from their seeds at test time).  The projection bias
+  is shifted by +1 as the reference's own comparisons do
+  (`tests/test_deconv_equivalence.py:69-76`), so the layer is well conditioned.
+
+`update_zero_*` fixtures hold whole blocks where the source is exactly zero, so the
+denominator is `eps` alone there and the ratios are of the order of 1e16: the regime the
+reference's comparisons avoid at the layer level, pinned here at the update boundary where
+float32 and float64 still agree.
 """
 
 import argparse
@@ -47,6 +58,11 @@ UPDATE_CASES = [
     ("brats512", dict(channels=512, ratio=4, groups=-1, kernel_size=(3, 3, 3)), 1, (3, 4, 3), True),
     ("later_iter", dict(channels=8, ratio=4, groups=-1, kernel_size=(3, 3, 3)), 2, (6, 5, 7), False),
     ("b3", dict(channels=6, ratio=4, groups=-1, kernel_size=(3, 3, 3)), 3, (9, 8, 7), True),
+    # whole zero neighbourhoods of the source (denominator = eps): see `zero_blocks`
+    ("zero_dw3d", dict(channels=6, ratio=4, groups=-1, kernel_size=(3, 3, 3)), 2, (10, 9, 12), True),
+    ("zero_dw2d_k5", dict(channels=4, ratio=4, groups=-1, kernel_size=(5, 5)), 2, (21, 24), True),
+    ("zero_later_iter", dict(channels=4, ratio=4, groups=-1, kernel_size=(3, 3, 3)), 1, (9, 8, 8), False),
+    ("zero_grouped", dict(channels=8, ratio=2, groups=2, kernel_size=(3, 3, 3)), 2, (8, 7, 6), True),
 ]
 
 LAYER_CASES = [
@@ -64,6 +80,18 @@ def _np(t):
     return None if t is None else t.detach().cpu().numpy()
 
 
+def zero_blocks(z, G, sc, first_iter):
+    """Make the source exactly zero on whole blocks: the first half of the leading spatial axis
+    for every channel, and the whole volume for the channels of group 0 in sample 0.  Before the
+    first iteration the source is `relu(z + bias)` with |bias| well below 2, so -2 does it."""
+    z = z.clone()
+    off = -2.0 if first_iter else 0.0
+    half = z.shape[2] // 2
+    z[:, :, :half] = off
+    z[0, :sc] = off
+    return z
+
+
 def update_case(ReferenceDeconv, name, kwargs, batch, spatial, first_iter, seed=0):
     torch.manual_seed(seed)
     ref = ReferenceDeconv(**kwargs)
@@ -79,6 +107,8 @@ def update_case(ReferenceDeconv, name, kwargs, batch, spatial, first_iter, seed=
         # later iterations get an already rectified, biased source and no bias
         z = torch.relu(torch.randn(batch, G * sc, *spatial) * 0.5 + 0.4)
         bias = None
+    if name.startswith("zero_"):
+        z = zero_blocks(z, G, sc, first_iter)
     h = torch.relu(ref.init.h0.detach() + 0.05)
     torch.manual_seed(seed + 2)
     gout = torch.randn(batch, G * sc, *spatial)
@@ -183,19 +213,60 @@ def cfg1_digest(ReferenceDeconv):
     print("cfg1_digest:", tuple(y64.shape))
 
 
+def cfg3_digest(ReferenceDeconv):
+    """3-D benchmark geometry, forward + backward: X (2,64,64,64,64) uniform, K = |N(0,1)|/27,
+    upstream gradient N(0,1), projection bias shifted by +1; float64 on the CPU."""
+    kwargs = dict(channels=64, ratio=4, groups=-1, kernel_size=(3, 3, 3))
+    torch.manual_seed(0)
+    ref = ReferenceDeconv(**kwargs)
+    with torch.no_grad():
+        ref.init.h0.copy_(torch.randn(64, 4, 3, 3, 3).abs() / 27)
+        ref.init.linear.linear.bias.add_(1.0)
+    state = {k: v.clone() for k, v in ref.state_dict().items()}
+    x = torch.rand(2, 64, 64, 64, 64, generator=torch.Generator().manual_seed(1))
+    gout = torch.randn(2, 256, 64, 64, 64, generator=torch.Generator().manual_seed(2))
+    mod = ref.double()
+    xl = x.double().requires_grad_(True)
+    y = mod(xl)
+    y.backward(gout.double())
+    yf, gxf = y.detach().flatten(), xl.grad.flatten()
+    ys, gs = 4093, 1021          # primes: the samples walk through every channel and row
+    np.savez_compressed(
+        os.path.join(HERE, "cfg3_digest.npz"),
+        h0=_np(state["init.h0"]), weight=_np(state["init.linear.linear.weight"]),
+        bias=_np(state["init.linear.linear.bias"]),
+        x_seed=1, gout_seed=2, x_shape=np.array(x.shape), gout_shape=np.array(gout.shape),
+        x_sum=float(x.double().sum()), gout_sum=float(gout.double().sum()),
+        y_stride=ys, gx_stride=gs,
+        y_sub_f64=_np(yf[::ys]), gx_sub_f64=_np(gxf[::gs]),
+        y_abs_max_f64=float(yf.abs().max()), gx_abs_max_f64=float(gxf.abs().max()),
+        y_sum_f64=float(yf.sum()), gx_sum_f64=float(gxf.sum()),
+        gh0_f64=_np(mod.init.h0.grad), gweight_f64=_np(mod.init.linear.linear.weight.grad),
+        gbias_f64=_np(mod.init.linear.linear.bias.grad),
+    )
+    print("cfg3_digest:", tuple(y.shape))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
+    ap.add_argument("--only", default="", help="comma-separated fixture names to (re)generate")
     args = ap.parse_args()
+    only = set(filter(None, args.only.split(",")))
     sys.path.insert(0, args.reference)
     from deconver.deconvolution.reference import ReferenceDeconv
 
     torch.set_num_threads(max(1, os.cpu_count() or 1))
     for case in UPDATE_CASES:
-        update_case(ReferenceDeconv, *case)
+        if not only or "update_" + case[0] in only:
+            update_case(ReferenceDeconv, *case)
     for case in LAYER_CASES:
-        layer_case(ReferenceDeconv, *case)
-    cfg1_digest(ReferenceDeconv)
+        if not only or case[0] in only:
+            layer_case(ReferenceDeconv, *case)
+    if not only or "cfg1_digest" in only:
+        cfg1_digest(ReferenceDeconv)
+    if not only or "cfg3_digest" in only:
+        cfg3_digest(ReferenceDeconv)
 
 
 if __name__ == "__main__":

@@ -102,3 +102,21 @@ def test_reconstruct_and_loss_shapes():
     assert x_hat.shape == (2, 12, 5, 4, 6)
     loss = m.loss(m.split_channels(x_hat), m.split_channels(s), m.split_channels(h))
     assert loss.shape == (6,) and float(loss.max()) < 1e-6
+
+
+def test_bench_reads_the_tracked_traffic_summary():
+    """`roofline.traffic` comes from the tracked ncu summary, scaled by the batch; both arms of
+    the benchmark print the same `config` object."""
+    import re
+
+    import bench
+
+    traffic, source = bench.load_traffic(2)
+    text = open(bench.TRAFFIC_FILE).read()
+    rows = re.findall(r"^#\s+\w+_kernel\s+(\d+)\s+(\d+)\s*$", text, re.M)
+    assert rows, "the summary lists the kernels it adds up"
+    total_mb = sum(int(a) + int(b) for a, b in rows)
+    assert traffic == 2 * total_mb * 1000 * 1000
+    assert "profiles/" in source
+    assert bench.config_of(4)["global_batch"] == 8
+    assert bench.config_of(1) == bench.config_of(1)

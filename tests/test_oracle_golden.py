@@ -90,3 +90,27 @@ def test_cfg1_digest():
     sub = y.flatten()[:: int(g["stride"])].numpy()
     assert max_norm_error(sub, g["y_sub_f64"]) < 1e-5
     assert abs(float(y.double().sum()) - float(g["y_sum_f64"])) < 1e-4 * abs(float(g["y_sum_f64"]))
+
+
+def test_cfg3_digest():
+    """The 3-D benchmark geometry, forward and backward, float32 on the CPU (about half a
+    minute): the oracle's port of the layer against the digest of the reference's float64 run."""
+    g = load_golden("cfg3_digest")
+    x = torch.rand(*[int(v) for v in g["x_shape"]],
+                   generator=torch.Generator().manual_seed(int(g["x_seed"])))
+    gout = torch.randn(*[int(v) for v in g["gout_shape"]],
+                       generator=torch.Generator().manual_seed(int(g["gout_seed"])))
+    assert abs(float(x.double().sum()) - float(g["x_sum"])) < 1e-6 * float(g["x_sum"])
+    assert abs(float(gout.double().sum()) - float(g["gout_sum"])) < 1e-3
+    x.requires_grad_(True)
+    w = _t(g["weight"], torch.float32).requires_grad_(True)
+    b = _t(g["bias"], torch.float32).requires_grad_(True)
+    h0 = _t(g["h0"], torch.float32).requires_grad_(True)
+    y = O.ndc_layer(x, w, b, h0, groups=64)
+    y.backward(gout)
+    ysub = y.detach().flatten()[:: int(g["y_stride"])].double().numpy()
+    assert np.abs(ysub - g["y_sub_f64"]).max() / float(g["y_abs_max_f64"]) < 1e-5
+    gsub = x.grad.flatten()[:: int(g["gx_stride"])].double().numpy()
+    assert np.abs(gsub - g["gx_sub_f64"]).max() / float(g["gx_abs_max_f64"]) < 1e-3
+    for key, p in (("gh0", h0), ("gweight", w), ("gbias", b)):
+        assert max_norm_error(p.grad.numpy(), g[f"{key}_f64"]) < 1e-3, key

@@ -108,7 +108,10 @@ def test_layer_matches_reference_fixture(dev, name):
     off so that it is a float32 product as on the CPU."""
     g = load_golden(name)
     if name.endswith("nobias_shift"):
-        pytest.skip("ill-conditioned on purpose (den = eps); covered at the update boundary")
+        # den = eps over whole neighbourhoods: one ulp in the projection flips ReLU masks, so
+        # the layer-level result is not comparable between any two float32 evaluations.  The
+        # same regime is pinned at the update boundary by the `update_zero_*` fixtures.
+        pytest.skip("ill-conditioned at the layer level; see the update_zero_* fixtures")
     old = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
     torch.backends.cudnn.allow_tf32 = False
     torch.backends.cuda.matmul.allow_tf32 = False
@@ -343,6 +346,110 @@ def test_gconv_adjoint_identity(dev):
     lhs = (ku.double() * v.double()).sum().item()
     rhs = (u.double() * av.double()).sum().item()
     assert abs(lhs - rhs) < 1e-5 * max(abs(lhs), 1.0)
+
+
+@pytest.mark.parametrize("case", [
+    # groups, m, sc, kernel, batch, spatial
+    (16, 1, 4, (3, 3, 3), 2, (9, 10, 21)),
+    (6, 1, 4, (5, 5), 2, (23, 37)),
+    (3, 4, 2, (3, 3, 3), 1, (6, 7, 8)),
+    (2, 3, 5, (3, 5, 3), 2, (5, 8, 6)),
+    (8, 1, 2, (7,), 3, (50,)),
+], ids=["dw3d", "dw2d_k5", "grouped", "aniso", "dw1d"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])
+def test_gconv_matches_oracle_operators(dev, case, dtype):
+    """`ndc_gconv` (K, A, and K with bias + ReLU folded into the load) against the oracle's
+    `K` and `A` in float64 (`deconver/deconvolution/kernels.py:728-759` in the reference)."""
+    G, m, sc, ks, B, spatial = case
+    gen = torch.Generator().manual_seed(77 + G + len(ks))
+    u = (torch.randn(B, G * sc, *spatial, generator=gen) * 0.5 + 0.2).to(dtype)
+    v = torch.randn(B, G * m, *spatial, generator=gen).to(dtype)
+    h = torch.rand(G * m, sc, *ks, generator=gen) / float(np.prod(ks))
+    bias = torch.randn(G * sc, generator=gen) * 0.2
+    tol = F32_TOL if dtype == torch.float32 else BF16_TOL
+    hd = h.to(dev)
+    ku = dcb.gconv(u.to(dev), hd, groups=G, m=m, sc=sc, adjoint=False)
+    av = dcb.gconv(v.to(dev), hd, groups=G, m=m, sc=sc, adjoint=True)
+    kb = dcb.gconv(u.to(dev), hd, groups=G, m=m, sc=sc, adjoint=False, relu_input=True,
+                   bias=bias.to(dev))
+    torch.cuda.synchronize()
+    assert ku.dtype == dtype and av.shape == (B, G * sc, *spatial)
+    s = torch.relu(u.double() + bias.double().view(1, -1, *([1] * len(ks))))
+    for got, ref in ((ku, O.K(u.double(), h.double(), G)), (av, O.A(v.double(), h.double(), G)),
+                     (kb, O.K(s, h.double(), G))):
+        assert max_norm_error(got.float().cpu().numpy(), ref.numpy()) < tol
+
+
+def _digest_layer(g, C, ks, dev, dtype):
+    mod = dcb.Deconv(C, ks, ratio=4, groups=-1)
+    mod.load_state_dict({
+        "init.h0": torch.from_numpy(g["h0"]),
+        "init.linear.linear.weight": torch.from_numpy(g["weight"]),
+        "init.linear.linear.bias": torch.from_numpy(g["bias"]),
+    })
+    return mod.to(device=dev, dtype=dtype)
+
+
+class _NoTF32:
+    """The projection is a library GEMM: make it a float32 product, as on the CPU."""
+
+    def __enter__(self):
+        self.old = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cudnn.allow_tf32 = False
+        torch.backends.cuda.matmul.allow_tf32 = False
+
+    def __exit__(self, *exc):
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = self.old
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, F32_TOL), (torch.bfloat16, BF16_TOL)],
+                         ids=["f32", "bf16"])
+def test_cfg1_layer_matches_reference_digest(dev, dtype, tol):
+    """The 2-D benchmark configuration itself, X (1,32,256,256), k=5x5, ratio 4, forward:
+    this library's layer against the digest of the reference's `ReferenceDeconv` (float64)."""
+    g = load_golden("cfg1_digest")
+    torch.manual_seed(int(g["x_seed"]))
+    x = torch.rand(*[int(v) for v in g["x_shape"]])
+    assert abs(float(x.double().sum()) - float(g["x_sum"])) < 1e-6 * float(g["x_sum"])
+    mod = _digest_layer(g, 32, (5, 5), dev, dtype)
+    with torch.no_grad(), _NoTF32():
+        y = mod(x.to(device=dev, dtype=dtype))
+    torch.cuda.synchronize()
+    yf = y.float().flatten().cpu()
+    scale = float(g["y_abs_max_f64"])
+    sub = yf[:: int(g["stride"])].double().numpy()
+    assert np.abs(sub - g["y_sub_f64"]).max() / scale < tol
+    assert abs(float(yf.double().sum()) - float(g["y_sum_f64"])) < 10 * tol * abs(float(g["y_sum_f64"]))
+
+
+@pytest.mark.parametrize("dtype,tol,gtol", [(torch.float32, F32_TOL, 1e-3),
+                                            (torch.bfloat16, BF16_TOL, BF16_TOL)],
+                         ids=["f32", "bf16"])
+def test_cfg3_layer_matches_reference_digest(dev, dtype, tol, gtol):
+    """The 3-D benchmark configuration itself, X (2,64,64,64,64), k=3x3x3, ratio 4, forward
+    and backward: output, input gradient (strided samples) and every parameter gradient (in
+    full) against the digest of a float64 run of the reference's `ReferenceDeconv`."""
+    g = load_golden("cfg3_digest")
+    x = torch.rand(*[int(v) for v in g["x_shape"]],
+                   generator=torch.Generator().manual_seed(int(g["x_seed"])))
+    gout = torch.randn(*[int(v) for v in g["gout_shape"]],
+                       generator=torch.Generator().manual_seed(int(g["gout_seed"])))
+    assert abs(float(x.double().sum()) - float(g["x_sum"])) < 1e-6 * float(g["x_sum"])
+    assert abs(float(gout.double().sum()) - float(g["gout_sum"])) < 1e-3
+    mod = _digest_layer(g, 64, (3, 3, 3), dev, dtype)
+    xd = x.to(device=dev, dtype=dtype).requires_grad_(True)
+    with _NoTF32():
+        y = mod(xd)
+        y.backward(gout.to(device=dev, dtype=dtype))
+    torch.cuda.synchronize()
+    ysub = y.detach().float().flatten()[:: int(g["y_stride"])].double().cpu().numpy()
+    assert np.abs(ysub - g["y_sub_f64"]).max() / float(g["y_abs_max_f64"]) < tol
+    gsub = xd.grad.float().flatten()[:: int(g["gx_stride"])].double().cpu().numpy()
+    assert np.abs(gsub - g["gx_sub_f64"]).max() / float(g["gx_abs_max_f64"]) < gtol
+    for key, p in (("gh0", mod.init.h0), ("gweight", mod.init.linear.linear.weight),
+                   ("gbias", mod.init.linear.linear.bias)):
+        err = max_norm_error(p.grad.float().cpu().numpy(), g[f"{key}_f64"])
+        assert err < gtol, f"{key} error {err:.3e}"
 
 
 def test_abi_status_codes_on_device(dev):

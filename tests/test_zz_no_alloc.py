@@ -5,7 +5,8 @@ forbids cudaMalloc after start-up) have no allocator to take the backward pass's
 from, so this entry point keeps the scratch in a fixed array inside the library.  The test
 calls it through the C ABI, twice in a row on different inputs, and checks every output
 against the regular `ndc_bwd` entry point (same kernels, caller-provided workspace): the
-results must be identical.  It also checks that a geometry beyond the built-in array is
+results must be identical, and the second call must leave the device's free memory and
+torch's allocator untouched.  It also checks that a geometry beyond the built-in array is
 refused with a status, not run.
 
 This file is named so that pytest collects it last.
@@ -61,10 +62,18 @@ def test_static_workspace_backward_matches_regular_backward(case):
                                bias.data_ptr(), gout.data_ptr(), *[t.data_ptr() for t in ref],
                                ws.data_ptr(), need, st))
         got = _outputs(x, z, h, bias)
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(dev)
+        held_before = torch.cuda.memory_allocated(dev)
         _lib.check(lib.ndc_bwd_static(desc, x.data_ptr(), z.data_ptr(), t1.data_ptr(),
                                       h.data_ptr(), bias.data_ptr(), gout.data_ptr(),
                                       *[t.data_ptr() for t in got], st))
         torch.cuda.synchronize()
+        if seed == 2:
+            # the array exists since the first call: this one takes no device memory at all,
+            # neither from the driver nor from torch's allocator
+            assert torch.cuda.mem_get_info(dev)[0] >= free_before
+            assert torch.cuda.memory_allocated(dev) == held_before
         for name, a, b in zip(("gx", "gz", "gh", "gb"), got, ref):
             assert torch.isfinite(b).all(), name
             assert torch.equal(a, b), f"{name} differs between ndc_bwd_static and ndc_bwd (seed {seed})"
