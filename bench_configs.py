@@ -320,7 +320,7 @@ def train_step_record(dc, steps=10, graph=False, per_gpu_batch=0):
     ndc_fwd = clock.total_ms()
     return dict(n_gpus=world, global_batch=16, per_gpu_batch=nb, dtype="bfloat16",
                 cuda_graph=bool(graph), steps=steps, ms_per_step=ms,
-                voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss),
+                voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss.detach()),
                 ndc_forward_ms_per_rank=ndc_fwd, params=sum(p.numel() for p in params))
 
 

@@ -73,7 +73,9 @@ __device__ __forceinline__ void cta_combine(float* scratch, const float (&acc)[N
     }
 }
 
-template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, int WQ>
+// PAIRS: gnum/gden go to ONE scratch tensor of (gden, gnum) pairs per voxel (the layout the
+// packed K kernel reads), at P.gnum; otherwise to two planar tensors.
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, int WQ, bool PAIRS = false>
 __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
     using L = RingSmem<KD, KH, KW>;
@@ -107,8 +109,8 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
     const T* tg = reinterpret_cast<const T*>(P.t1) + bx;
     const T* zg = reinterpret_cast<const T*>(P.z) + bz;
     const T* gg = reinterpret_cast<const T*>(P.gout) + bz;
-    float* gng = P.gnum + bz;
-    float* gdg = P.gden + bz;
+    float* gng = P.gnum + (PAIRS ? 2 * bz : bz);
+    float* gdg = PAIRS ? nullptr : P.gden + bz;
     T* dirg = P.gz ? reinterpret_cast<T*>(P.gz) + bz : nullptr;
 
     float* wA = smem + lay.wA;
@@ -218,8 +220,20 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
                     gnv[v] = gn;
                     if (w0 + v >= W) { gnv[v] = 0.0f; gdv[v] = 0.0f; }
                 }
-                store_strip_global<float, VEC, VA>(gng + j * SP + off, w0, W, gnv);
-                store_strip_global<float, VEC, VA>(gdg + j * SP + off, w0, W, gdv);
+                if (PAIRS) {
+                    float* dst = gng + 2 * (j * SP + off + w0);
+                    if (VEC) {
+                        reinterpret_cast<float4*>(dst)[0] = make_float4(gdv[0], gnv[0], gdv[1], gnv[1]);
+                        reinterpret_cast<float4*>(dst)[1] = make_float4(gdv[2], gnv[2], gdv[3], gnv[3]);
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < VA; ++v)
+                            if (w0 + v < W) { dst[2 * v] = gdv[v]; dst[2 * v + 1] = gnv[v]; }
+                    }
+                } else {
+                    store_strip_global<float, VEC, VA>(gng + j * SP + off, w0, W, gnv);
+                    store_strip_global<float, VEC, VA>(gdg + j * SP + off, w0, W, gdv);
+                }
                 if (dirg) store_strip_global<T, VEC, VA>(dirg + j * SP + off, w0, W, dv);
             }
         }
@@ -560,6 +574,308 @@ __global__ void __launch_bounds__(NT, 384 / NT) kconv_kernel(const KconvParams P
         for (int k = 0; k < NW; ++k) sbuf[slot * LD + k * SCH + jch] = accw[k];
         __syncthreads();
         float* out = P.partial[which] + (long long)blockIdx.x * kPartialStride;
+        for (int k = tid; k < KT * SCH; k += NT) {
+            float s = 0.0f;
+            for (int i = 0; i < NG; ++i) s += sbuf[i * LD + k];
+            out[k] = s;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// K applied to BOTH scratch tensors at once, packed.  The source is the tensor of (gden, gnum)
+// pairs ratio_kernel<PAIRS> writes; every multiply-add is a two-lane `fma.rn.f32x2` whose low
+// lane works on gden and whose high lane works on gnum:
+//
+//     running sums    (gt1, gx)[q]      += (gden, gnum)[j, q + tau - pad] * (h, h)[j, tau]
+//     correlations    (cD, cN)[j, tau]  += (t1, x)[q] * (gden, gnum)[j, q + tau - pad]
+//
+// so the source window is used as loaded (a 64-bit shared-memory element is a ready pair), the
+// filter is staged duplicated, and the saved (t1, x) strips are paired once per plane.  Half
+// the multiply-add instructions of two separate passes; the filter gradient needs cD + cN.
+struct Kconv2Params {
+    const float* in;        // (gden, gnum) pairs: [(b*C + c)*4 + j][voxel][2]
+    float* gt1;             // K(gden), float32 scratch, or NULL
+    void* gx;               // K(gnum), storage type, or NULL
+    const void* t1;         // saved t1 and x: the strips the correlations pair with
+    const void* x;
+    float* partial;         // [cta][kPartialStride] records of cD + cN, or NULL
+    const float* h;
+    int C, D, H, W;
+    Tiling t;
+};
+
+constexpr int VK2 = 4;     // voxels per strip of the packed K kernel
+
+template <int KD, int KH, int KW>
+struct Kconv2Smem {
+    static constexpr int PD = KD / 2, PH = KH / 2;
+    static constexpr int KWP = (KW + 1) / 2 * 2;   // taps per (kh, j, kd), padded to an even count
+    static constexpr int NSB = KD > 1 ? 3 : 1;     // planes p, p+1 (landed) and p+2 (in flight)
+    int wK, sbuf, desc, total_floats, RS, plane_s, pitch2, NC2;
+    __host__ __device__ Kconv2Smem(const Tiling& t, int nthreads) {
+        RS = t.TH + 2 * PH;
+        pitch2 = 2 * t.pitch;                      // a row of pairs
+        plane_s = SCH * RS * pitch2;
+        NC2 = 2 * t.NQ;                            // 16-byte chunks (two voxels) per row
+        int o = 0;
+        wK = o; o += KH * SCH * KD * KWP * 2;      // [kh][j][kd][tap] duplicated weights
+        o = (o + 3) / 4 * 4;
+        sbuf = o; o += NSB * plane_s;
+        desc = o; o += 2 * (SCH * RS * NC2);
+        total_floats = o;
+        // room for the end-of-kernel combine (nthreads/4 rows of taps*4 + 1 floats)
+        const int red = (nthreads / SCH) * (KD * KH * KW * SCH + 1);
+        if (total_floats - sbuf < red) total_floats = sbuf + red;
+    }
+};
+
+// 16-byte chunk c of a row of pairs -> its place in shared memory.  The eight lanes of a
+// quarter-warp read chunks two apart (strips of 4 voxels = 2 chunks); folding bit 3 of the chunk
+// index into bit 0 sends them to eight different 16-byte bank groups.
+__device__ __forceinline__ int swz2(int chunk) { return chunk ^ ((chunk >> 3) & 1); }
+
+template <typename T, int KD, int KH, int KW, int NT, bool VEC, bool WGRAD, int WQ>
+__global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv2_kernel(const Kconv2Params P) {
+    constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
+    constexpr int VK = VK2;
+    using L = Kconv2Smem<KD, KH, KW>;
+    constexpr int KWP = L::KWP, NSB = L::NSB;
+    constexpr int NG = NT / SCH;                 // strip slots per CTA
+    constexpr int NW = WGRAD ? KT : 1;           // correlation accumulators (pairs) per thread
+    constexpr int NWIN = VK + 4;                 // window pairs held: voxels w0-2 .. w0+VK+1
+    static_assert(KD > 1 && PW <= 2, "packed K kernel: marching kernels with up to 5 columns");
+    extern __shared__ __align__(16) float smem[];
+    const L lay(P.t, NT);
+    const int tid = threadIdx.x;
+    const int NQ = WQ ? WQ : P.t.NQ, NSV = NQ, pitch2 = 2 * (WQ ? row_pitch(4 * WQ) : P.t.pitch),
+              W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
+    const long long HW = (long long)P.H * W, SP = HW * D;
+    const int NC2 = 2 * NQ;
+
+    int blk = blockIdx.x;
+    const int th = blk % P.t.nth; blk /= P.t.nth;
+    const int dch = blk % P.t.ndc; blk /= P.t.ndc;
+    const int bc = blk;
+    const int c = bc % P.C;
+    const int h0 = th * P.t.TH, H = P.H;
+    const int TH = min(P.t.TH, H - h0);
+    const int d0 = dch * P.t.DC, d1 = min(D, d0 + P.t.DC);
+    const int RS = lay.RS;
+    const long long bx = (long long)bc * SP;
+
+    const float* ing = P.in + 2 * (long long)bc * SCH * SP;
+    float* gt1g = P.gt1 ? P.gt1 + bx : nullptr;
+    T* gxg = P.gx ? reinterpret_cast<T*>(P.gx) + bx : nullptr;
+    const T* t1g = reinterpret_cast<const T*>(P.t1) + bx;
+    const T* xg = reinterpret_cast<const T*>(P.x) + bx;
+
+    float* wK = smem + lay.wK;
+    float* sbuf = smem + lay.sbuf;
+    ChunkDesc* desc = reinterpret_cast<ChunkDesc*>(smem + lay.desc);
+    for (int i = tid; i < NSB * lay.plane_s; i += NT) sbuf[i] = 0.0f;
+    {
+        const float* hc = P.h + (long long)c * SCH * KT;
+        for (int i = tid; i < KH * SCH * KD * KWP; i += NT) {   // wK[kh][j][kd][kw] = (w, w)
+            const int kw = i % KWP, kd = (i / KWP) % KD, j = (i / (KWP * KD)) % SCH, kh = i / (KWP * KD * SCH);
+            const float v = kw < KW ? hc[j * KT + (kd * KH + kh) * KW + kw] : 0.0f;
+            wK[2 * i] = v; wK[2 * i + 1] = v;
+        }
+    }
+    // loader table: .goff = voxel offset in the plane (-1: nothing to load), .soff = float offset
+    // of the destination chunk in a plane buffer | (valid voxels << 26)
+    const int nz = SCH * RS * NC2;
+    for (int id = tid; id < nz; id += NT) {
+        const int c2 = id % NC2, t = id / NC2, r = t % RS, ch = t / RS;
+        const int h = h0 - PH + r, w = 2 * c2, n = min(2, W - w);
+        ChunkDesc dsc;
+        dsc.goff = (h < 0 || h >= H || n <= 0) ? -1 : (int)(ch * SP + (long long)h * W) + w;
+        dsc.soff = ((ch * RS + r) * pitch2 + (swz2(c2 + 2) << 2)) | (max(n, 0) << 26);
+        desc[id] = dsc;
+    }
+    const int lane = tid & 31;
+    const int jch = (lane >> 3) & 3;                       // this thread's source channel
+    const int slot = (tid >> 5) * 8 + (lane & 7);          // strip slot inside the CTA
+    const int n_items = TH * NSV;
+    f32x2 accw[NW];
+#pragma unroll
+    for (int k = 0; k < NW; ++k) accw[k] = pack2(0.0f, 0.0f);
+    __syncthreads();
+
+    const int p_first = d0 - PD, p_last = d1 - 1 + PD;
+    auto copy_plane = [&](int plane) {
+        const float* src = ing + 2 * (long long)plane * HW;
+        float* dst = sbuf + ((plane - p_first) % NSB) * lay.plane_s;
+        for (int id = tid; id < nz; id += NT) {
+            const ChunkDesc dsc = desc[id];
+            if (dsc.goff < 0) continue;
+            float* q = dst + (dsc.soff & 0x3ffffff);
+            const float* g = src + 2 * (long long)dsc.goff;
+            if (VEC) {
+                const unsigned sa = (unsigned)__cvta_generic_to_shared(q);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(g) : "memory");
+            } else {
+                const bool two = ((dsc.soff >> 26) & 3) > 1;
+                *reinterpret_cast<float4*>(q) =
+                    make_float4(__ldg(g), __ldg(g + 1), two ? __ldg(g + 2) : 0.0f, two ? __ldg(g + 3) : 0.0f);
+            }
+        }
+        if (VEC) cp_async_commit();
+    };
+    auto wait_but_newest = [&]() { if (VEC) asm volatile("cp.async.wait_group 1;\n" ::: "memory"); };
+
+    const bool k_ok = slot < n_items;
+    const int k_row = k_ok ? slot / NSV : 0, k_strip = k_ok ? slot % NSV : 0;
+    // shared-memory offsets (floats) of the window chunks of this strip: chunks 2*strip+1 ..
+    // 2*strip+VK/2+2 of a row hold voxels w0-2 .. w0+VK+1
+    int qo[NWIN / 2];
+#pragma unroll
+    for (int q = 0; q < NWIN / 2; ++q) qo[q] = swz2((VK / 2) * k_strip + 1 + q) << 2;
+
+    f32x2 kacc[KD][VK], auxs[WGRAD ? KD : 1][VK];
+#pragma unroll
+    for (int a = 0; a < KD; ++a)
+#pragma unroll
+        for (int v = 0; v < VK; ++v) kacc[a][v] = pack2(0.0f, 0.0f);
+
+    // one source row of this thread's channel feeds KD output planes (and their correlations);
+    // output plane p+PD-kd lives in slot (R + PD - kd) mod KD, R = rotation of this step
+    auto accumulate = [&](auto rot, int p) {
+        constexpr int R = decltype(rot)::value;
+        const float* sp = sbuf + ((p - p_first) % NSB) * lay.plane_s + (jch * RS + k_row) * pitch2;
+#pragma unroll
+        for (int kh = 0; kh < KH; ++kh) {
+            f32x2 sv[NWIN];
+#pragma unroll
+            for (int q = 0; q < NWIN / 2; ++q) {
+                const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(sp + kh * pitch2 + qo[q]);
+                sv[2 * q] = t.x; sv[2 * q + 1] = t.y;
+            }
+#pragma unroll
+            for (int kd = 0; kd < KD; ++kd) {
+                f32x2 w[KWP];
+#pragma unroll
+                for (int q = 0; q < KWP / 2; ++q) {
+                    const ulonglong2 t = *reinterpret_cast<const ulonglong2*>(
+                        wK + 2 * (((kh * SCH + jch) * KD + kd) * KWP + 2 * q));
+                    w[2 * q] = t.x; w[2 * q + 1] = t.y;
+                }
+                constexpr int sl = (R + PD - kd + 2 * KD) % KD;
+#pragma unroll
+                for (int kw = 0; kw < KW; ++kw) {
+                    f32x2 a = accw[WGRAD ? (kd * KH + kh) * KW + kw : 0];
+#pragma unroll
+                    for (int v = 0; v < VK; ++v) {
+                        fma2(kacc[sl][v], sv[v + kw - PW + 2], w[kw]);
+                        if (WGRAD) fma2(a, auxs[WGRAD ? sl : 0][v], sv[v + kw - PW + 2]);
+                    }
+                    if (WGRAD) accw[WGRAD ? (kd * KH + kh) * KW + kw : 0] = a;
+                }
+            }
+        }
+    };
+    // add the four channel lanes' partial sums; every lane ends up owning one voxel of the strip
+    auto finish = [&](int q, bool store, const f32x2 (&part)[VK]) {
+        const bool hi = jch & 2, odd = jch & 1;
+        f32x2 h2[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float sl_, sh_, kl, kh_;
+            unpack2(hi ? part[i] : part[2 + i], sl_, sh_);
+            unpack2(hi ? part[2 + i] : part[i], kl, kh_);
+            kl += __shfl_xor_sync(0xffffffffu, sl_, 16);
+            kh_ += __shfl_xor_sync(0xffffffffu, sh_, 16);
+            h2[i] = pack2(kl, kh_);
+        }
+        float sl_, sh_, o_t, o_x;
+        unpack2(odd ? h2[0] : h2[1], sl_, sh_);
+        unpack2(odd ? h2[1] : h2[0], o_t, o_x);
+        o_t += __shfl_xor_sync(0xffffffffu, sl_, 8);
+        o_x += __shfl_xor_sync(0xffffffffu, sh_, 8);
+        if (store) {
+            const int w = VK * k_strip + (hi ? 2 : 0) + (odd ? 1 : 0);
+            if (w < W) {
+                const long long off = (long long)q * HW + (long long)(h0 + k_row) * W + w;
+                if (gt1g) gt1g[off] = o_t;
+                if (gxg) gxg[off] = from_f32<T>(o_x);
+            }
+        }
+    };
+    // (t1, x) strip of plane q, raw; zero outside the chunk
+    const long long aux_off = (long long)(h0 + k_row) * W + VK * k_strip;
+    auto aux_raw = [&](int q, Raw4<T> (&dst)[2]) {
+        if (WGRAD && k_ok && q >= d0 && q < d1) {
+            dst[0] = load_strip_raw<T, VEC>(t1g + (long long)q * HW + aux_off - VK * k_strip, VK * k_strip, W);
+            dst[1] = load_strip_raw<T, VEC>(xg + (long long)q * HW + aux_off - VK * k_strip, VK * k_strip, W);
+        } else {
+            dst[0].v = {}; dst[1].v = {};
+        }
+    };
+    auto aux_pairs = [&](const Raw4<T> (&raw)[2], f32x2 (&dst)[VK]) {
+        const float4 a = to_float4(raw[0]), b = to_float4(raw[1]);
+        dst[0] = pack2(a.x, b.x); dst[1] = pack2(a.y, b.y);
+        dst[2] = pack2(a.z, b.z); dst[3] = pack2(a.w, b.w);
+    };
+
+    // planes are requested two steps ahead of their use
+    auto plane_ok = [&](int q) { return q >= 0 && q < D && q <= p_last; };
+    if (plane_ok(p_first)) copy_plane(p_first); else if (VEC) cp_async_commit();
+    if (plane_ok(p_first + 1)) copy_plane(p_first + 1); else if (VEC) cp_async_commit();
+    // plane q lives in slot (q - p_first) mod KD: at the first step (rotation 0) output plane
+    // p_first + PD - kd is slot (PD - kd) mod KD
+    if (WGRAD) {
+#pragma unroll
+        for (int kd = 0; kd < KD; ++kd) {
+            Raw4<T> raw[2];
+            aux_raw(p_first + PD - kd, raw);
+            aux_pairs(raw, auxs[WGRAD ? (PD - kd + KD) % KD : 0]);
+        }
+    }
+    wait_but_newest();
+    __syncthreads();
+
+    auto step = [&](auto rot, int p) {
+        constexpr int R = decltype(rot)::value;
+        constexpr int DONE = (R - PD + 2 * KD) % KD;     // slot of plane p-PD, reused for p+1+PD
+        Raw4<T> aux_next[2];                               // strips of plane p+1+PD, in flight
+        aux_raw(p + 1 + PD, aux_next);
+        if (plane_ok(p + 2)) copy_plane(p + 2); else if (VEC) cp_async_commit();
+        const int qdone = p - PD;
+        if (k_ok && p >= 0 && p < D) accumulate(rot, p);
+        if (qdone >= d0 && qdone < d1) finish(qdone, k_ok, kacc[DONE]);
+#pragma unroll
+        for (int v = 0; v < VK; ++v) kacc[DONE][v] = pack2(0.0f, 0.0f);
+        if (WGRAD) aux_pairs(aux_next, auxs[WGRAD ? DONE : 0]);
+        wait_but_newest();   // plane p+1 has landed; p+2 may still be in flight
+        __syncthreads();
+    };
+    int p = p_first;
+    while (p <= p_last) {
+        step(std::integral_constant<int, 0>{}, p++);
+        if (p > p_last) break;
+        step(std::integral_constant<int, 1 % KD>{}, p++);
+        if (p > p_last) break;
+        if (KD > 2) step(std::integral_constant<int, 2 % KD>{}, p++);
+        if (KD > 3) {
+            if (p > p_last) break;
+            step(std::integral_constant<int, 3 % KD>{}, p++);
+            if (p > p_last) break;
+            if (KD > 4) step(std::integral_constant<int, 4 % KD>{}, p++);
+        }
+    }
+    if (WGRAD && P.partial) {
+        // per-CTA combine in a fixed order: slot-major scratch rows of taps*4 (+1 pad) floats
+        constexpr int LD = KT * SCH + 1;
+        if (VEC) cp_async_wait_all();
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < NW; ++k) {
+            float lo, up;
+            unpack2(accw[k], lo, up);
+            sbuf[slot * LD + k * SCH + jch] = lo + up;
+        }
+        __syncthreads();
+        float* out = P.partial + (long long)blockIdx.x * kPartialStride;
         for (int k = tid; k < KT * SCH; k += NT) {
             float s = 0.0f;
             for (int i = 0; i < NG; ++i) s += sbuf[i * LD + k];
