@@ -605,14 +605,12 @@ struct Kconv2Params {
     Tiling t;
 };
 
-constexpr int VK2 = 4;     // voxels per strip of the packed K kernel
-
 template <int KD, int KH, int KW>
 struct Kconv2Smem {
     static constexpr int PD = KD / 2, PH = KH / 2;
     static constexpr int KWP = (KW + 1) / 2 * 2;   // taps per (kh, j, kd), padded to an even count
     static constexpr int NSB = KD > 1 ? 3 : 1;     // planes p, p+1 (landed) and p+2 (in flight)
-    int wK, sbuf, desc, total_floats, RS, plane_s, pitch2, NC2;
+    int wK, sbuf, total_floats, RS, plane_s, pitch2, NC2;
     __host__ __device__ Kconv2Smem(const Tiling& t, int nthreads) {
         RS = t.TH + 2 * PH;
         pitch2 = 2 * t.pitch;                      // a row of pairs
@@ -622,7 +620,6 @@ struct Kconv2Smem {
         wK = o; o += KH * SCH * KD * KWP * 2;      // [kh][j][kd][tap] duplicated weights
         o = (o + 3) / 4 * 4;
         sbuf = o; o += NSB * plane_s;
-        desc = o; o += 2 * (SCH * RS * NC2);
         total_floats = o;
         // room for the end-of-kernel combine (nthreads/4 rows of taps*4 + 1 floats)
         const int red = (nthreads / SCH) * (KD * KH * KW * SCH + 1);
@@ -631,25 +628,34 @@ struct Kconv2Smem {
 };
 
 // 16-byte chunk c of a row of pairs -> its place in shared memory.  The eight lanes of a
-// quarter-warp read chunks two apart (strips of 4 voxels = 2 chunks); folding bit 3 of the chunk
-// index into bit 0 sends them to eight different 16-byte bank groups.
-__device__ __forceinline__ int swz2(int chunk) { return chunk ^ ((chunk >> 3) & 1); }
+// quarter-warp read chunks VK/2 apart (strips of VK voxels); folding bits 3.. of the chunk index
+// into the low bits sends them to eight different 16-byte bank groups.
+template <int VK> __device__ __forceinline__ int swz2(int chunk) {
+    return chunk ^ ((chunk >> 3) & (VK == 8 ? 3 : 1));
+}
 
-template <typename T, int KD, int KH, int KW, int NT, bool VEC, bool WGRAD, int WQ>
-__global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv2_kernel(const Kconv2Params P) {
+// Threads per SM the packed K kernel is built for, by CTA size and strip length.
+template <int NT, int VK> constexpr int kconv2_min_blocks() {
+    return VK == 8 ? (NT >= 256 ? 1 : NT >= 128 ? 2 : NT >= 64 ? 4 : 8)
+                   : (NT >= 256 ? 1 : NT >= 192 ? 2 : NT >= 128 ? 3 : 4);
+}
+
+template <typename T, int KD, int KH, int KW, int NT, int VK, int MAXC, bool VEC, bool WGRAD, int WQ>
+__global__ void __launch_bounds__(NT, kconv2_min_blocks<NT, VK>()) kconv2_kernel(const Kconv2Params P) {
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
-    constexpr int VK = VK2;
     using L = Kconv2Smem<KD, KH, KW>;
     constexpr int KWP = L::KWP, NSB = L::NSB;
     constexpr int NG = NT / SCH;                 // strip slots per CTA
     constexpr int NW = WGRAD ? KT : 1;           // correlation accumulators (pairs) per thread
     constexpr int NWIN = VK + 4;                 // window pairs held: voxels w0-2 .. w0+VK+1
-    static_assert(KD > 1 && PW <= 2, "packed K kernel: marching kernels with up to 5 columns");
+    constexpr int VO = VK / 4;                   // voxels a lane owns after the channel lanes add up
+    static_assert(KD > 1 && PW <= 2 && (VK == 4 || VK == 8), "packed K kernel: marching kernels with up to 5 columns");
     extern __shared__ __align__(16) float smem[];
     const L lay(P.t, NT);
     const int tid = threadIdx.x;
-    const int NQ = WQ ? WQ : P.t.NQ, NSV = NQ, pitch2 = 2 * (WQ ? row_pitch(4 * WQ) : P.t.pitch),
+    const int NQ = WQ ? WQ : P.t.NQ, pitch2 = 2 * (WQ ? row_pitch(4 * WQ) : P.t.pitch),
               W = WQ ? 4 * WQ : P.W, D = P.D;   // WQ > 0: the width is a compile-time constant
+    const int NSV = (4 * NQ + VK - 1) / VK;      // strips per row
     const long long HW = (long long)P.H * W, SP = HW * D;
     const int NC2 = 2 * NQ;
 
@@ -672,7 +678,6 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
 
     float* wK = smem + lay.wK;
     float* sbuf = smem + lay.sbuf;
-    ChunkDesc* desc = reinterpret_cast<ChunkDesc*>(smem + lay.desc);
     for (int i = tid; i < NSB * lay.plane_s; i += NT) sbuf[i] = 0.0f;
     {
         const float* hc = P.h + (long long)c * SCH * KT;
@@ -682,16 +687,20 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
             wK[2 * i] = v; wK[2 * i + 1] = v;
         }
     }
-    // loader table: .goff = voxel offset in the plane (-1: nothing to load), .soff = float offset
-    // of the destination chunk in a plane buffer | (valid voxels << 26)
+    // this thread's chunks of a source plane (fixed for the CTA's lifetime): voxel offset in the
+    // plane (-1: nothing to load) and float offset of the destination chunk | (valid voxels << 26)
     const int nz = SCH * RS * NC2;
-    for (int id = tid; id < nz; id += NT) {
-        const int c2 = id % NC2, t = id / NC2, r = t % RS, ch = t / RS;
-        const int h = h0 - PH + r, w = 2 * c2, n = min(2, W - w);
-        ChunkDesc dsc;
-        dsc.goff = (h < 0 || h >= H || n <= 0) ? -1 : (int)(ch * SP + (long long)h * W) + w;
-        dsc.soff = ((ch * RS + r) * pitch2 + (swz2(c2 + 2) << 2)) | (max(n, 0) << 26);
-        desc[id] = dsc;
+    int cg_off[MAXC], cs_off[MAXC];
+#pragma unroll
+    for (int i = 0; i < MAXC; ++i) {
+        const int id = tid + i * NT;
+        cg_off[i] = -1; cs_off[i] = 0;
+        if (id < nz) {
+            const int c2 = id % NC2, t = id / NC2, r = t % RS, ch = t / RS;
+            const int h = h0 - PH + r, w = 2 * c2, n = min(2, W - w);
+            if (h >= 0 && h < H && n > 0) cg_off[i] = (int)(ch * SP + (long long)h * W) + w;
+            cs_off[i] = ((ch * RS + r) * pitch2 + (swz2<VK>(c2 + 2) << 2)) | (max(n, 0) << 26);
+        }
     }
     const int lane = tid & 31;
     const int jch = (lane >> 3) & 3;                       // this thread's source channel
@@ -706,16 +715,16 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
     auto copy_plane = [&](int plane) {
         const float* src = ing + 2 * (long long)plane * HW;
         float* dst = sbuf + ((plane - p_first) % NSB) * lay.plane_s;
-        for (int id = tid; id < nz; id += NT) {
-            const ChunkDesc dsc = desc[id];
-            if (dsc.goff < 0) continue;
-            float* q = dst + (dsc.soff & 0x3ffffff);
-            const float* g = src + 2 * (long long)dsc.goff;
+#pragma unroll
+        for (int i = 0; i < MAXC; ++i) {
+            if (cg_off[i] < 0) continue;
+            float* q = dst + (cs_off[i] & 0x3ffffff);
+            const float* g = src + 2 * (long long)cg_off[i];
             if (VEC) {
                 const unsigned sa = (unsigned)__cvta_generic_to_shared(q);
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(sa), "l"(g) : "memory");
             } else {
-                const bool two = ((dsc.soff >> 26) & 3) > 1;
+                const bool two = ((cs_off[i] >> 26) & 3) > 1;
                 *reinterpret_cast<float4*>(q) =
                     make_float4(__ldg(g), __ldg(g + 1), two ? __ldg(g + 2) : 0.0f, two ? __ldg(g + 3) : 0.0f);
             }
@@ -726,11 +735,11 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
 
     const bool k_ok = slot < n_items;
     const int k_row = k_ok ? slot / NSV : 0, k_strip = k_ok ? slot % NSV : 0;
-    // shared-memory offsets (floats) of the window chunks of this strip: chunks 2*strip+1 ..
-    // 2*strip+VK/2+2 of a row hold voxels w0-2 .. w0+VK+1
+    // shared-memory offsets (floats) of the window chunks of this strip: chunks
+    // (VK/2)*strip + 1 .. + VK/2 + 2 of a row hold voxels w0-2 .. w0+VK+1
     int qo[NWIN / 2];
 #pragma unroll
-    for (int q = 0; q < NWIN / 2; ++q) qo[q] = swz2((VK / 2) * k_strip + 1 + q) << 2;
+    for (int q = 0; q < NWIN / 2; ++q) qo[q] = swz2<VK>((VK / 2) * k_strip + 1 + q) << 2;
 
     f32x2 kacc[KD][VK], auxs[WGRAD ? KD : 1][VK];
 #pragma unroll
@@ -760,7 +769,7 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
                         wK + 2 * (((kh * SCH + jch) * KD + kd) * KWP + 2 * q));
                     w[2 * q] = t.x; w[2 * q + 1] = t.y;
                 }
-                constexpr int sl = (R + PD - kd + 2 * KD) % KD;
+                const int sl = (R + PD - kd + 2 * KD) % KD;
 #pragma unroll
                 for (int kw = 0; kw < KW; ++kw) {
                     f32x2 a = accw[WGRAD ? (kd * KH + kh) * KW + kw : 0];
@@ -774,47 +783,71 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
             }
         }
     };
-    // add the four channel lanes' partial sums; every lane ends up owning one voxel of the strip
+    // add the four channel lanes' partial sums; every lane ends up owning VO voxels of the strip
     auto finish = [&](int q, bool store, const f32x2 (&part)[VK]) {
         const bool hi = jch & 2, odd = jch & 1;
-        f32x2 h2[2];
+        f32x2 h2[VK / 2];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            float sl_, sh_, kl, kh_;
-            unpack2(hi ? part[i] : part[2 + i], sl_, sh_);
-            unpack2(hi ? part[2 + i] : part[i], kl, kh_);
-            kl += __shfl_xor_sync(0xffffffffu, sl_, 16);
-            kh_ += __shfl_xor_sync(0xffffffffu, sh_, 16);
-            h2[i] = pack2(kl, kh_);
+        for (int i = 0; i < VK / 2; ++i) {
+            float s_lo, s_up, k_lo, k_up;
+            unpack2(hi ? part[i] : part[VK / 2 + i], s_lo, s_up);
+            unpack2(hi ? part[VK / 2 + i] : part[i], k_lo, k_up);
+            k_lo += __shfl_xor_sync(0xffffffffu, s_lo, 16);
+            k_up += __shfl_xor_sync(0xffffffffu, s_up, 16);
+            h2[i] = pack2(k_lo, k_up);
         }
-        float sl_, sh_, o_t, o_x;
-        unpack2(odd ? h2[0] : h2[1], sl_, sh_);
-        unpack2(odd ? h2[1] : h2[0], o_t, o_x);
-        o_t += __shfl_xor_sync(0xffffffffu, sl_, 8);
-        o_x += __shfl_xor_sync(0xffffffffu, sh_, 8);
+        float o_t[VO], o_x[VO];
+#pragma unroll
+        for (int i = 0; i < VO; ++i) {
+            float s_lo, s_up;
+            unpack2(odd ? h2[i] : h2[VO + i], s_lo, s_up);
+            unpack2(odd ? h2[VO + i] : h2[i], o_t[i], o_x[i]);
+            o_t[i] += __shfl_xor_sync(0xffffffffu, s_lo, 8);
+            o_x[i] += __shfl_xor_sync(0xffffffffu, s_up, 8);
+        }
         if (store) {
-            const int w = VK * k_strip + (hi ? 2 : 0) + (odd ? 1 : 0);
-            if (w < W) {
-                const long long off = (long long)q * HW + (long long)(h0 + k_row) * W + w;
-                if (gt1g) gt1g[off] = o_t;
-                if (gxg) gxg[off] = from_f32<T>(o_x);
+            const int w = VK * k_strip + (hi ? VK / 2 : 0) + (odd ? VO : 0);
+            const long long off = (long long)q * HW + (long long)(h0 + k_row) * W + w;
+            if (VEC && VO == 2) {
+                if (w < W) {
+                    if (gt1g) *reinterpret_cast<float2*>(gt1g + off) = make_float2(o_t[0], o_t[VO - 1]);
+                    if (gxg) {
+                        if (sizeof(T) == 4) *reinterpret_cast<float2*>(gxg + off) = make_float2(o_x[0], o_x[VO - 1]);
+                        else *reinterpret_cast<__nv_bfloat162*>(gxg + off) = __floats2bfloat162_rn(o_x[0], o_x[VO - 1]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < VO; ++i)
+                    if (w + i < W) {
+                        if (gt1g) gt1g[off + i] = o_t[i];
+                        if (gxg) gxg[off + i] = from_f32<T>(o_x[i]);
+                    }
             }
         }
     };
-    // (t1, x) strip of plane q, raw; zero outside the chunk
-    const long long aux_off = (long long)(h0 + k_row) * W + VK * k_strip;
-    auto aux_raw = [&](int q, Raw4<T> (&dst)[2]) {
+    // (t1, x) strips of plane q, raw; zero outside the chunk
+    const T* t1_row = t1g + (long long)(h0 + k_row) * W;
+    const T* x_row = xg + (long long)(h0 + k_row) * W;
+    auto aux_raw = [&](int q, Raw4<T> (&dst)[2 * VO]) {
         if (WGRAD && k_ok && q >= d0 && q < d1) {
-            dst[0] = load_strip_raw<T, VEC>(t1g + (long long)q * HW + aux_off - VK * k_strip, VK * k_strip, W);
-            dst[1] = load_strip_raw<T, VEC>(xg + (long long)q * HW + aux_off - VK * k_strip, VK * k_strip, W);
+#pragma unroll
+            for (int i = 0; i < VO; ++i) {
+                dst[i] = load_strip_raw<T, VEC>(t1_row + (long long)q * HW, VK * k_strip + 4 * i, W);
+                dst[VO + i] = load_strip_raw<T, VEC>(x_row + (long long)q * HW, VK * k_strip + 4 * i, W);
+            }
         } else {
-            dst[0].v = {}; dst[1].v = {};
+#pragma unroll
+            for (int i = 0; i < 2 * VO; ++i) dst[i].v = {};
         }
     };
-    auto aux_pairs = [&](const Raw4<T> (&raw)[2], f32x2 (&dst)[VK]) {
-        const float4 a = to_float4(raw[0]), b = to_float4(raw[1]);
-        dst[0] = pack2(a.x, b.x); dst[1] = pack2(a.y, b.y);
-        dst[2] = pack2(a.z, b.z); dst[3] = pack2(a.w, b.w);
+    auto aux_pairs = [&](const Raw4<T> (&raw)[2 * VO], f32x2 (&dst)[VK]) {
+#pragma unroll
+        for (int i = 0; i < VO; ++i) {
+            const float4 a = to_float4(raw[i]), b = to_float4(raw[VO + i]);
+            dst[4 * i] = pack2(a.x, b.x); dst[4 * i + 1] = pack2(a.y, b.y);
+            dst[4 * i + 2] = pack2(a.z, b.z); dst[4 * i + 3] = pack2(a.w, b.w);
+        }
     };
 
     // planes are requested two steps ahead of their use
@@ -826,7 +859,7 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
     if (WGRAD) {
 #pragma unroll
         for (int kd = 0; kd < KD; ++kd) {
-            Raw4<T> raw[2];
+            Raw4<T> raw[2 * VO];
             aux_raw(p_first + PD - kd, raw);
             aux_pairs(raw, auxs[WGRAD ? (PD - kd + KD) % KD : 0]);
         }
@@ -837,7 +870,7 @@ __global__ void __launch_bounds__(NT, NT >= 256 ? 1 : (NT >= 128 ? 2 : 4)) kconv
     auto step = [&](auto rot, int p) {
         constexpr int R = decltype(rot)::value;
         constexpr int DONE = (R - PD + 2 * KD) % KD;     // slot of plane p-PD, reused for p+1+PD
-        Raw4<T> aux_next[2];                               // strips of plane p+1+PD, in flight
+        Raw4<T> aux_next[2 * VO];                          // strips of plane p+1+PD, in flight
         aux_raw(p + 1 + PD, aux_next);
         if (plane_ok(p + 2)) copy_plane(p + 2); else if (VEC) cp_async_commit();
         const int qdone = p - PD;

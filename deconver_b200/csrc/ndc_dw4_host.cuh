@@ -139,19 +139,28 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
 
 // Threads (and prefetch registers, in quads per thread) of the three backward kernels.
 // Bands: a CTA owns a band of rows of every plane.  kconv: 48 strip slots x 4 channel lanes.
+// Kconv2NT / Kconv2VK: threads and strip length of the packed K kernel (3x3x3 volumes): a strip
+// of VK voxels per group of 4 channel lanes.  Kconv2WideNT: the CTA used instead for rows of more
+// than 64 voxels (0: none), where the narrow one would be left with bands of one or two rows.
+// Kconv2MAXC: 16-byte source chunks a thread copies per plane, at most (bands shrink to fit).
 struct BwdBands {
     static constexpr int RatioNT = 128, RatioMAXX = 2, KconvNT = 192, GzNT = 128, GzMAXX = 4;
+    static constexpr int Kconv2NT = 128, Kconv2VK = 8, Kconv2MAXC = 6, Kconv2WideNT = 256, Kconv2WideMAXC = 5;
 };
 // Rows: one-row planes of NQ 4-voxel strips (2-D images run as volumes, see FwdRows).
 template <int NQ_> struct BwdRows {
     static constexpr int RatioNT = NQ_, RatioMAXX = 1, KconvNT = 2 * NQ_, GzNT = NQ_, GzMAXX = 1;
+    // (not used: the row kernels keep two K passes)
+    static constexpr int Kconv2NT = 4 * NQ_, Kconv2VK = 4, Kconv2MAXC = 4, Kconv2WideNT = 0, Kconv2WideMAXC = 0;
 };
 // Small volumes (3x3x3): narrower CTAs where they cover the same bands (see FwdSmall).
 struct BwdSmall16 {   // bands of up to 64 strips of 4 (16 x 16 rows)
     static constexpr int RatioNT = 64, RatioMAXX = 2, KconvNT = 128, GzNT = 64, GzMAXX = 2;
+    static constexpr int Kconv2NT = 128, Kconv2VK = 8, Kconv2MAXC = 6, Kconv2WideNT = 0, Kconv2WideMAXC = 0;
 };
 struct BwdSmall8 {    // bands of up to 32 strips of 4 (8 x 8 rows)
     static constexpr int RatioNT = 32, RatioMAXX = 1, KconvNT = 32, GzNT = 32, GzMAXX = 1;
+    static constexpr int Kconv2NT = 32, Kconv2VK = 8, Kconv2MAXC = 5, Kconv2WideNT = 0, Kconv2WideMAXC = 0;
 };
 constexpr int kGzCS = 1;        // channel split of gz_kernel (2 was measured no faster)
 
@@ -204,11 +213,42 @@ inline bool plan_kconv(int D, int H, int W, long long BC, Tiling& t, size_t& sme
     return true;
 }
 
+// The packed K kernel (both scratch tensors in one pass) serves the 3x3x3 volumes.
+template <int KD, int KH, int KW>
+constexpr bool packed_kconv() { return KD == 3 && KH == 3 && KW == 3; }
+
+template <int KD, int KH, int KW, int NT, int VK, int MAXC>
+inline bool plan_kconv2(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
+    constexpr int PH = KH / 2;
+    if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
+    t.NQ = (W + 3) / 4;
+    t.pitch = row_pitch(W);
+    const int NSV = (4 * t.NQ + VK - 1) / VK;
+    int TH = std::min(H, (NT / SCH) / NSV);            // one strip per group of 4 channel lanes
+    auto bytes = [&](int th) {
+        Tiling q = t; q.TH = th;
+        return (size_t)Kconv2Smem<KD, KH, KW>(q, NT).total_floats * sizeof(float);
+    };
+    auto chunks = [&](int th) { return SCH * (th + 2 * PH) * 2 * t.NQ; };
+    constexpr int per_sm = kconv2_min_blocks<NT, VK>();
+    const size_t target = (kSmemMax - 8 * 1024) / per_sm;
+    while (TH > 1 && (bytes(TH) > target || chunks(TH) > MAXC * NT ||
+                      SCH * (TH + 2 * PH) * 2 * t.pitch >= (1 << 26)))
+        --TH;
+    if (TH < 1 || bytes(TH) > target || chunks(TH) > MAXC * NT) return false;
+    t.nth = (H + TH - 1) / TH;
+    t.TH = (H + t.nth - 1) / t.nth;
+    plan_depth(KD, D, BC * t.nth, 6, t, per_sm);
+    smem_bytes = bytes(t.TH);
+    return true;
+}
+
 struct BwdPlan {
     Tiling ratio, kconv, gz;
     size_t smem_ratio, smem_kconv, smem_gz;
     size_t off_gnum, off_gden, off_gt1, off_gxtmp, off_pa, off_pa2, off_pb, bytes;
     long long n_ratio, n_kconv, n_gz;   // CTAs (kconv: per tensor; = partial records)
+    int kconv_wide;                     // packed K kernel: the wide CTA was planned
     int rows;                           // 0: band kernels; else the rows class planned
     int small;                          // 0, or the small-volume class planned (16 or 8)
 };
@@ -219,7 +259,20 @@ inline bool plan_bwd(const Geo& g, BwdPlan& p) {
     if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, S::RatioNT, S::RatioMAXX, 0, 0, 56 * 1024,
                                512 / S::RatioNT, p.ratio, p.smem_ratio))
         return false;
-    if (!plan_kconv<KD, KH, KW, S::KconvNT>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
+    p.kconv_wide = 0;
+    if constexpr (packed_kconv<KD, KH, KW>()) {
+        bool ok = false;
+        if constexpr (S::Kconv2WideNT > 0) {
+            if (g.W > 64) {
+                ok = plan_kconv2<KD, KH, KW, S::Kconv2WideNT, S::Kconv2VK, S::Kconv2WideMAXC>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv);
+                p.kconv_wide = ok ? 1 : 0;
+            }
+        }
+        if (!ok && !plan_kconv2<KD, KH, KW, S::Kconv2NT, S::Kconv2VK, S::Kconv2MAXC>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv))
+            return false;
+    } else {
+        if (!plan_kconv<KD, KH, KW, S::KconvNT>(g.D, g.H, g.W, BC, p.kconv, p.smem_kconv)) return false;
+    }
     // gz_kernel also double-buffers its strips of z and of the direct term (16 bytes each)
     if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 1, S::GzNT, S::GzMAXX,
                                gz_combine_floats<KD, KH, KW, kGzCS>(S::GzNT),
@@ -330,12 +383,42 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;
         P.gnum = gnum; P.gden = gden; P.gz = gz;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.ratio; P.eps = g.eps; P.relu = g.relu;
-        auto kern = ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, VEC, WQ>;
+        auto kern = ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, VEC, WQ, packed_kconv<KD, KH, KW>()>;
         NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
         kern<<<(unsigned)p.n_ratio, S::RatioNT, p.smem_ratio, st>>>(P);
         launched();
     }
-    {
+    if constexpr (packed_kconv<KD, KH, KW>()) {
+        Kconv2Params P;
+        P.in = gnum;                          // (gden, gnum) pairs fill the gnum | gden area
+        P.gt1 = (gz || gh) ? gt1 : nullptr;
+        P.gx = gx;
+        P.t1 = t1; P.x = x;
+        P.partial = gh ? pa : nullptr;
+        P.h = h; P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.kconv;
+        auto run = [&](auto nt, auto maxc) -> cudaError_t {
+            constexpr int NT = decltype(nt)::value, VK = S::Kconv2VK, MAXC = decltype(maxc)::value;
+            if (gh) {
+                auto kern = kconv2_kernel<T, KD, KH, KW, NT, VK, MAXC, VEC, true, WQ>;
+                NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
+                kern<<<(unsigned)p.n_kconv, NT, p.smem_kconv, st>>>(P);
+            } else {
+                auto kern = kconv2_kernel<T, KD, KH, KW, NT, VK, MAXC, VEC, false, WQ>;
+                NDC_CUDA_TRY(set_smem(kern, p.smem_kconv));
+                kern<<<(unsigned)p.n_kconv, NT, p.smem_kconv, st>>>(P);
+            }
+            return cudaSuccess;
+        };
+        if constexpr (S::Kconv2WideNT > 0) {
+            if (p.kconv_wide)
+                NDC_CUDA_TRY(run(std::integral_constant<int, S::Kconv2WideNT>{}, std::integral_constant<int, S::Kconv2WideMAXC>{}));
+            else
+                NDC_CUDA_TRY(run(std::integral_constant<int, S::Kconv2NT>{}, std::integral_constant<int, S::Kconv2MAXC>{}));
+        } else {
+            NDC_CUDA_TRY(run(std::integral_constant<int, S::Kconv2NT>{}, std::integral_constant<int, S::Kconv2MAXC>{}));
+        }
+        launched();
+    } else {
         KconvParams P;
         int n = 0;
         if (gz || gh) {
@@ -385,7 +468,7 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
     if (gh || gb) {
         ReduceParams P;
         P.partial_a = gh ? pa : nullptr;
-        P.partial_a2 = gh ? pa2 : nullptr;
+        P.partial_a2 = (gh && !packed_kconv<KD, KH, KW>()) ? pa2 : nullptr;   // packed: one record set
         P.partial_b = pb;
         P.ctas_per_bc_a = (long long)p.kconv.ndc * p.kconv.nth;
         P.ctas_per_bc_b = (long long)p.gz.ndc * p.gz.nth;
