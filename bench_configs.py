@@ -85,12 +85,14 @@ class LayerClock:
         return sum(a.elapsed_time(b) for a, b in self.pairs if b is not None)
 
 
-def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, depths_dec, ks):
+def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, depths_dec, ks, own_norm=True):
     import deconver.deconver as dm
     import deconver_b200
     from deconver.deconvolution.deconv import Deconv as RefDeconv
 
     norm = torch.nn.InstanceNorm3d if spatial_dims == 3 else torch.nn.InstanceNorm2d
+    if use_b200 and own_norm:   # the same operator on this library's kernels
+        norm = deconver_b200.InstanceNorm3d if spatial_dims == 3 else deconver_b200.InstanceNorm2d
     dm.Deconv = deconver_b200.Deconv if use_b200 else RefDeconv
     try:
         torch.manual_seed(0)

@@ -19,7 +19,8 @@ FLAG_FORCE_GENERIC = 1
 SYMBOLS = (
     "ndc_version", "ndc_last_error", "ndc_status_string", "ndc_launch_count", "ndc_query",
     "ndc_fwd", "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_bwd_static", "ndc_gconv",
-    "ndc_probe_fp32_fma",
+    "ndc_probe_fp32_fma", "ndc_inorm_workspace_bytes", "ndc_inorm_last_error", "ndc_inorm_fwd",
+    "ndc_inorm_bwd",
 )
 
 
@@ -78,6 +79,15 @@ def load():
     lib.ndc_probe_fp32_fma.restype = ctypes.c_int
     lib.ndc_probe_fp32_fma.argtypes = [ctypes.c_int32, ctypes.c_int32, fp, ctypes.c_size_t,
                                        ctypes.POINTER(ctypes.c_uint64), vp]
+    lib.ndc_inorm_workspace_bytes.restype = ctypes.c_size_t
+    lib.ndc_inorm_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32]
+    lib.ndc_inorm_last_error.restype = ctypes.c_char_p
+    lib.ndc_inorm_fwd.restype = ctypes.c_int
+    lib.ndc_inorm_fwd.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp,
+                                  fp, fp, ctypes.c_float, vp, fp, vp, ctypes.c_size_t, vp]
+    lib.ndc_inorm_bwd.restype = ctypes.c_int
+    lib.ndc_inorm_bwd.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp,
+                                  vp, fp, fp, vp, fp, fp, vp, ctypes.c_size_t, vp]
     _lib = lib
     return lib
 

@@ -173,6 +173,31 @@ int ndc_bwd_static(const NdcDesc *desc, const void *x, const void *z, const void
                    float *gh, float *gb, void *stream);
 
 /*
+ * Instance normalisation of a (batch, channels, spatial...) tensor, forward and backward:
+ *     y = (x - mean) * rstd [* weight[c] + bias[c]],   rstd = 1 / sqrt(var + eps),
+ * mean and biased variance taken over the `spatial` positions of each (sample, channel) slab.
+ * Replaces the `norm1` / `norm2` modules of the reference's `DeconverBlock`
+ * (deconver/deconver.py:52-65), for which its configurations pass torch's InstanceNorm{2,3}d;
+ * that library kernel runs one block per slab, which leaves most of the GPU idle at the small
+ * per-GPU batches of the batch-sharded training step.  Here every slab is split over as many
+ * CTAs as fill the device.  `weight`, `bias` (float32, per channel) may be NULL.  `mean_rstd`
+ * receives (mean, rstd) per slab (2 * batch * channels floats) for the backward call, or may be
+ * NULL in forward.  `workspace`: ndc_inorm_workspace_bytes(batch, channels) bytes of device
+ * memory, 16-byte aligned, contents undefined before and after.  `gweight`, `gbias` (float32,
+ * overwritten) may be NULL.  Sums use a fixed order: results are bitwise reproducible.
+ * Errors: status code, message from ndc_inorm_last_error().
+ */
+size_t ndc_inorm_workspace_bytes(int32_t batch, int32_t channels);
+const char *ndc_inorm_last_error(void);
+int ndc_inorm_fwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, const void *x,
+                  const float *weight, const float *bias, float eps, void *y, float *mean_rstd,
+                  void *workspace, size_t workspace_bytes, void *stream);
+int ndc_inorm_bwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, const void *x,
+                  const void *gy, const float *weight, const float *mean_rstd, void *gx,
+                  float *gweight, float *gbias, void *workspace, size_t workspace_bytes,
+                  void *stream);
+
+/*
  * Measurement aid; no counterpart in the reference project.  Launches one kernel of
  * register-only fused multiply-add chains (4 blocks of 256 threads per multiprocessor, 8
  * independent chains per thread, iters x 64 instructions per thread) on `stream`: plain

@@ -1,0 +1,88 @@
+"""Instance normalisation kernels against PyTorch's `instance_norm` evaluated in float64.
+
+The modules stand in for the `norm` class of the reference's blocks (`DeconverBlock.norm1/2`,
+`deconver/deconver.py:52-65`; its configurations pass `torch.nn.InstanceNorm{2,3}d`).
+Tolerances (max-norm relative): float32 1e-5 forward and 1e-4 backward; bfloat16 storage 2e-2.
+"""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import deconver_b200 as dcb
+from conftest import max_norm_error
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # batch, channels, spatial, affine
+    (2, 64, (64, 64, 64), False),      # stage-1 geometry of the 3-D network at a per-GPU batch of 2
+    (2, 512, (8, 8, 8), False),
+    (3, 5, (7, 9, 11), True),          # odd sizes: scalar path
+    (1, 3, (37,), True),
+    (4, 32, (256, 256), False),
+    (1, 1, (130000,), False),          # one slab, many parts
+    (2, 6, (1, 1, 2), True),           # two positions per slab
+]
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    dcb.load_library()
+    return torch.device("cuda:0")
+
+
+def _reference(x, w, b, g, eps):
+    x64 = x.double().requires_grad_(True)
+    w64 = None if w is None else w.double().requires_grad_(True)
+    b64 = None if b is None else b.double().requires_grad_(True)
+    y = F.instance_norm(x64, weight=w64, bias=b64, eps=eps)
+    y.backward(g.double())
+    return y.detach(), x64.grad, None if w64 is None else w64.grad, None if b64 is None else b64.grad
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "b%d_c%d_%s%s" % (
+    c[0], c[1], "x".join(map(str, c[2])), "_affine" if c[3] else ""))
+@pytest.mark.parametrize("dtype,tol,gtol", [(torch.float32, 1e-5, 1e-4), (torch.bfloat16, 2e-2, 2e-2)],
+                         ids=["f32", "bf16"])
+def test_instance_norm_matches_float64(dev, case, dtype, tol, gtol):
+    B, C, S, affine = case
+    gen = torch.Generator().manual_seed(B * 100 + C)
+    # a mean well away from zero: the variance must not lose digits to cancellation
+    x = (torch.randn(B, C, *S, generator=gen) * 0.7 + 5.0).to(dtype)
+    g = torch.randn(B, C, *S, generator=gen).to(dtype)
+    w = (torch.rand(C, generator=gen) + 0.5) if affine else None
+    b = torch.randn(C, generator=gen) if affine else None
+    ref = _reference(x.float(), w, b, g.float(), 1e-5)
+    xd = x.to(dev).requires_grad_(True)
+    wd = None if w is None else w.to(dev).requires_grad_(True)
+    bd = None if b is None else b.to(dev).requires_grad_(True)
+    y = dcb.instance_norm(xd, wd, bd, 1e-5)
+    y.backward(g.to(dev))
+    torch.cuda.synchronize()
+    assert y.dtype == dtype and y.shape == x.shape
+    assert max_norm_error(y.detach().float().cpu().numpy(), ref[0].numpy()) < tol
+    assert max_norm_error(xd.grad.float().cpu().numpy(), ref[1].numpy()) < gtol
+    if affine:
+        assert max_norm_error(wd.grad.cpu().numpy(), ref[2].numpy()) < max(gtol, 1e-4)
+        assert max_norm_error(bd.grad.cpu().numpy(), ref[3].numpy()) < max(gtol, 1e-4)
+
+
+def test_module_matches_torch_module_and_is_reproducible(dev):
+    torch.manual_seed(0)
+    x = torch.randn(2, 16, 12, 10, 20, device=dev)
+    mine, theirs = dcb.InstanceNorm3d(16), torch.nn.InstanceNorm3d(16)
+    assert list(mine.state_dict()) == list(theirs.state_dict())
+    a, b = mine(x), mine(x)
+    assert torch.equal(a, b)
+    assert max_norm_error(a.cpu().numpy(), theirs(x).double().cpu().numpy()) < 1e-5
+    affine = dcb.InstanceNorm2d(8, affine=True).to(dev)
+    assert sorted(affine.state_dict()) == sorted(torch.nn.InstanceNorm2d(8, affine=True).state_dict())
+    with pytest.raises(ValueError):
+        affine(x)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        dcb.instance_norm(torch.randn(1, 2, 4))
+    with pytest.raises(NotImplementedError):
+        dcb.InstanceNorm1d(4, track_running_stats=True)

@@ -45,13 +45,14 @@ def reference():
     return deconver, deconver_module, ReferenceDeconv
 
 
-def _network(reference, layer_cls, dev):
+def _network(reference, layer_cls, dev, norm=None):
     dc, module, _ = reference
     original = module.Deconv
     module.Deconv = layer_cls
     try:
         torch.manual_seed(0)
-        return dc.Deconver(**NETWORK).to(dev).eval()
+        kwargs = dict(NETWORK, norm=norm) if norm is not None else NETWORK
+        return dc.Deconver(**kwargs).to(dev).eval()
     finally:
         module.Deconv = original
 
@@ -61,13 +62,16 @@ def _errors(a, b):
     return (diff.max() / b.double().abs().max().clamp_min(1e-30)).item()
 
 
-def test_network_on_this_layer_is_as_close_to_float64_as_the_original(reference):
+@pytest.mark.parametrize("own_norm", [False, True], ids=["layer", "layer_and_norm"])
+def test_network_on_this_layer_is_as_close_to_float64_as_the_original(reference, own_norm):
+    """`own_norm`: the network is also given this library's InstanceNorm3d as its `norm` class."""
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     dcb.load_library()
     dev = torch.device("cuda:0")
     _, _, ReferenceDeconv = reference
     old = _network(reference, ReferenceDeconv, dev)
-    new = _network(reference, dcb.Deconv, dev)
+    new = _network(reference, dcb.Deconv, dev, norm=dcb.InstanceNorm3d if own_norm else None)
+    assert any(isinstance(m, dcb.InstanceNorm3d) for m in new.modules()) == own_norm
     assert any(isinstance(m, dcb.Deconv) for m in new.modules())
     assert not any(isinstance(m, ReferenceDeconv) for m in new.modules())
     assert list(old.state_dict()) == list(new.state_dict())
