@@ -15,6 +15,8 @@ and no CPU path: tensors must live on a CUDA device and be float32 or bfloat16.
 """
 
 import contextlib
+import ctypes
+import warnings
 from typing import Optional, Sequence
 
 import torch
@@ -93,6 +95,27 @@ def kernels_apply(x: Tensor, m: int, sc: int, kernel_size: Sequence[int]) -> boo
     return _lib.load().ndc_query(desc, None) == _lib.NDC_OK
 
 
+_warned_generic = set()
+
+
+def _warn_if_generic(desc, flags: int) -> None:
+    """Depthwise ratio-4 problems normally run on the tiled kernels; tell the user (once per
+    geometry class) when one falls outside them and takes the much slower generic kernels."""
+    if flags & _lib.FLAG_FORCE_GENERIC or desc.m != 1 or desc.sc != 4:
+        return
+    key = (desc.kD, desc.kH, desc.kW, desc.W > 256, desc.dtype)
+    if key in _warned_generic:
+        return
+    path = ctypes.c_int32(-1)
+    if _lib.load().ndc_query(desc, ctypes.byref(path)) == _lib.NDC_OK and path.value == _lib.PATH_GENERIC:
+        _warned_generic.add(key)
+        warnings.warn(
+            f"deconver_b200: depthwise ratio-4 update with kernel ({desc.kD},{desc.kH},{desc.kW}) on "
+            f"({desc.D},{desc.H},{desc.W}) runs on the generic kernels (about 20x slower per voxel); "
+            "the tiled kernels cover 3x3x3 volumes up to 256 columns and 5x5 / 3x3 images up to 512",
+            RuntimeWarning, stacklevel=3)
+
+
 def _require(t: Optional[Tensor], name: str, like: Tensor) -> None:
     if t is None:
         return
@@ -152,6 +175,7 @@ class DeconvUpdate(torch.autograd.Function):
         ks = tuple(h.shape[2:])
         flags = _flags   # read once: backward runs later, on an autograd thread
         desc = _desc(x, groups, m, sc, ks, eps, relu_input, flags)
+        _warn_if_generic(desc, flags)
         hf, bf = _f32(h), _f32(bias)
         out = torch.empty_like(z)
         t1 = torch.empty_like(x)
