@@ -148,3 +148,14 @@ def test_planner_on_random_geometries(lib):
         # per-CTA records of the filter-gradient reduction (a few percent at most)
         bound = int(4 * elems * (2 * sc + 2 * m) * 1.05) + 64 * 1024 * 1024 + 4096 * batch * groups
         assert 0 < need <= bound, (need, bound, batch, groups, m, sc, spatial, ks)
+
+
+def test_instance_norm_and_probe_entry_points_validate_without_a_gpu(lib):
+    assert lib.ndc_inorm_workspace_bytes(2, 64) == 2 * 64 * 64 * 2 * 4
+    assert lib.ndc_inorm_workspace_bytes(0, 64) == 0
+    assert lib.ndc_inorm_fwd(2, 64, 4096, 0, None, None, None, 1e-5, None, None, None, 0, None) == 1
+    assert b"NULL" in lib.ndc_inorm_last_error()
+    assert lib.ndc_inorm_bwd(2, 64, 4096, 0, None, None, None, None, None, None, None, None, 0,
+                             None) == 1
+    assert lib.ndc_probe_fp32_fma(0, 0, None, 0, None, None) == 1
+    assert b"iters" in lib.ndc_last_error()

@@ -120,3 +120,19 @@ def test_bench_reads_the_tracked_traffic_summary():
     assert "profiles/" in source
     assert bench.config_of(4)["global_batch"] == 8
     assert bench.config_of(1) == bench.config_of(1)
+
+
+def test_instance_norm_module_host_logic():
+    """Constructor, state-dict keys and refusals of the instance-norm modules (no GPU needed)."""
+    import deconver_b200 as dcb
+
+    for mine, theirs in ((dcb.InstanceNorm3d(8), torch.nn.InstanceNorm3d(8)),
+                         (dcb.InstanceNorm2d(8, affine=True), torch.nn.InstanceNorm2d(8, affine=True))):
+        assert sorted(mine.state_dict()) == sorted(theirs.state_dict())
+        mine.load_state_dict(theirs.state_dict())
+    with pytest.raises(NotImplementedError):
+        dcb.InstanceNorm3d(8, track_running_stats=True)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        dcb.InstanceNorm1d(4)(torch.randn(2, 4, 10))          # there is no CPU path
+    with pytest.raises(ValueError):
+        dcb.InstanceNorm2d(4)(torch.randn(2, 4, 10))
