@@ -162,10 +162,7 @@ struct BwdSmall8 {    // bands of up to 32 strips of 4 (8 x 8 rows)
     static constexpr int RatioNT = 32, RatioMAXX = 1, KconvNT = 32, GzNT = 32, GzMAXX = 1;
     static constexpr int Kconv2NT = 32, Kconv2VK = 8, Kconv2MAXC = 5, Kconv2WideNT = 0, Kconv2WideMAXC = 0;
 };
-#ifndef NDC_GZ_CS
-#define NDC_GZ_CS 1
-#endif
-constexpr int kGzCS = NDC_GZ_CS;        // channel split of gz_kernel (2 was measured no faster)
+constexpr int kGzCS = 1;        // channel split of gz_kernel (2 was measured no faster)
 
 // Band height for the kernels that only hold single-channel rings (ratio: 2 tensors, gz: 1).
 template <int KD, int KH, int KW>
