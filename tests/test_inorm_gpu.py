@@ -23,7 +23,7 @@ CASES = [
     (1, 3, (37,), True),
     (4, 32, (256, 256), False),
     (1, 1, (130000,), False),          # one slab, many parts
-    (2, 6, (1, 1, 2), True),           # two positions per slab
+    (2, 6, (1, 2, 3), True),           # six positions per slab
 ]
 
 
