@@ -73,10 +73,18 @@ __device__ __forceinline__ void cta_combine(float* scratch, const float (&acc)[N
     }
 }
 
-// PAIRS: gnum/gden go to ONE scratch tensor of (gden, gnum) pairs per voxel (the layout the
-// packed K kernel reads), at P.gnum; otherwise to two planar tensors.
-template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, int WQ, bool PAIRS = false>
+// MODE says what the per-voxel epilogue after the two adjoint sweeps produces:
+//   kRatioPlanar   backward: gnum, gden as two planar float32 scratch tensors, direct term
+//   kRatioPairs    backward: ONE scratch tensor of (gden, gnum) pairs per voxel at P.gnum (the
+//                  layout the packed K kernel reads), direct term
+//   kRatioForward  forward:  out = (s * n) / d into P.gz (storage type); P.gout is not read.
+//                  This is the second half of the two-launch forward (t1 = K(s) comes from
+//                  ksrc_kernel), used where it is faster than the fused fwd_kernel.
+enum RatioMode { kRatioPlanar = 0, kRatioPairs = 1, kRatioForward = 2 };
+
+template <typename T, int KD, int KH, int KW, int NT, int MAXX, bool VEC, int WQ, int MODE = kRatioPlanar>
 __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P) {
+    constexpr bool PAIRS = MODE == kRatioPairs, FWD = MODE == kRatioForward;
     constexpr int PD = KD / 2, PH = KH / 2, PW = KW / 2, KT = KD * KH * KW;
     using L = RingSmem<KD, KH, KW>;
     constexpr int RING = L::RING;
@@ -108,9 +116,9 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
     const T* xg = reinterpret_cast<const T*>(P.x) + bx;
     const T* tg = reinterpret_cast<const T*>(P.t1) + bx;
     const T* zg = reinterpret_cast<const T*>(P.z) + bz;
-    const T* gg = reinterpret_cast<const T*>(P.gout) + bz;
-    float* gng = P.gnum + (PAIRS ? 2 * bz : bz);
-    float* gdg = PAIRS ? nullptr : P.gden + bz;
+    const T* gg = FWD ? nullptr : reinterpret_cast<const T*>(P.gout) + bz;
+    float* gng = FWD ? nullptr : P.gnum + (PAIRS ? 2 * bz : bz);
+    float* gdg = (PAIRS || FWD) ? nullptr : P.gden + bz;
     T* dirg = P.gz ? reinterpret_cast<T*>(P.gz) + bz : nullptr;
 
     float* wA = smem + lay.wA;
@@ -173,11 +181,11 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
             const int hrow = h0 + a_row, w0 = VA * a_q;
             const long long off = (long long)d * HW + hrow * RWZ;
             // global strips first: their latency hides behind the tap sweep
-            Raw4<T> zraw[SCH], graw[SCH];   // converted in the epilogue
+            Raw4<T> zraw[SCH], graw[FWD ? 1 : SCH];   // converted in the epilogue
 #pragma unroll
             for (int j = 0; j < SCH; ++j) {
                 zraw[j] = load_strip_raw<T, VEC>(zg + j * SP + off, w0, W);
-                graw[j] = load_strip_raw<T, VEC>(gg + j * SP + off, w0, W);
+                if (!FWD) graw[FWD ? 0 : j] = load_strip_raw<T, VEC>(gg + j * SP + off, w0, W);
             }
             // accumulators hold channel pairs (2jp, 2jp+1) of one voxel
             f32x2 an2[SCH / 2][VA], ad2[SCH / 2][VA];
@@ -206,7 +214,17 @@ __global__ void __launch_bounds__(NT, 512 / NT) ratio_kernel(const RatioParams P
             for (int j = 0; j < SCH; ++j) {
                 float dv[VA], zj[VA], gj[VA], gnv[VA], gdv[VA];
                 raw_to_array(zraw[j], zj);
-                raw_to_array(graw[j], gj);
+                if (FWD) {
+#pragma unroll
+                    for (int v = 0; v < VA; ++v) {
+                        float s = zj[v] + bj[j];
+                        if (P.relu) s = fmaxf(s, 0.0f);
+                        dv[v] = fast_div(s * lane_of(an2[j / 2][v], j & 1), lane_of(ad2[j / 2][v], j & 1));
+                    }
+                    store_strip_global<T, VEC, VA>(dirg + j * SP + off, w0, W, dv);
+                    continue;
+                }
+                raw_to_array(graw[FWD ? 0 : j], gj);
 #pragma unroll
                 for (int v = 0; v < VA; ++v) {
                     float s = zj[v] + bj[j];

@@ -2,7 +2,9 @@
 //
 //     s = relu(z + b);  t1 = K(s);  out = (s * (A(x) + eps)) / (A(t1) + eps)
 //
-// in ONE kernel.  t1 never makes a round trip through HBM: each CTA marches through its depth
+// in ONE kernel.  This is the forward of 2-D image batches (5x5 and 3x3 kernels, marching down
+// the image rows or band by band); 3x3x3 volumes take two launches instead (ksrc_kernel, then
+// ratio_kernel in its forward mode), which was measured faster on every volume size.  t1 never makes a round trip through HBM: each CTA marches through its depth
 // chunk and keeps the planes it needs in shared-memory rings.  Per step p (a source plane):
 //
 //   prefetch   z plane p+1 and x plane p-PD into registers, raw (global loads in flight;

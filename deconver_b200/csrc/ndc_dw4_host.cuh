@@ -4,6 +4,7 @@
 #include <algorithm>
 
 #include "ndc_dw4_fwd.cuh"
+#include "ndc_dw4_ksrc.cuh"
 #include "ndc_dw4_bwd.cuh"
 
 namespace ndc {
@@ -28,17 +29,12 @@ constexpr size_t kSmemMax = 227 * 1024;
 
 // Launch shape per kernel geometry.
 template <int KD, int KH, int KW> struct FwdShape;
-template <> struct FwdShape<3, 3, 3> { static constexpr int NT = 256, MAXZ = 5, MAXX = 1, MINB = 2; };
 template <> struct FwdShape<1, 5, 5> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
 template <> struct FwdShape<1, 3, 3> { static constexpr int NT = 256, MAXZ = 1, MAXX = 1, MINB = 2; };
 // 2-D image batches run as volumes of one-row planes: rows become the marching axis,
 // so nothing is recomputed between row bands and the loads of the next row overlap the work
 // on this one.  A CTA is as wide as one row has 4-voxel strips.
 template <int NT_> struct FwdRows { static constexpr int NT = NT_, MAXZ = 4, MAXX = 1, MINB = 384 / NT_; };
-// Small volumes (3x3x3): a 256-thread CTA would mostly idle on a band of 32, 16 or 8 short rows,
-// so narrower CTAs are used where they cover the same band (more CTAs per SM instead).
-template <int NT_> struct FwdSmall { static constexpr int NT = NT_, MAXZ = 5, MAXX = 1, MINB = 512 / NT_; };
-
 inline bool shape_supported(int kD, int kH, int kW) {
     return (kD == 3 && kH == 3 && kW == 3) || (kD == 1 && kH == 5 && kW == 5) ||
            (kD == 1 && kH == 3 && kW == 3);
@@ -153,7 +149,8 @@ template <int NQ_> struct BwdRows {
     // (not used: the row kernels keep two K passes)
     static constexpr int Kconv2NT = 4 * NQ_, Kconv2VK = 4, Kconv2MAXC = 4, Kconv2WideNT = 0, Kconv2WideMAXC = 0;
 };
-// Small volumes (3x3x3): narrower CTAs where they cover the same bands (see FwdSmall).
+// Small volumes (3x3x3): narrower CTAs where they cover the same bands as the default ones
+// (a wide CTA would mostly idle on a band of 16 or 8 short rows).
 struct BwdSmall16 {   // bands of up to 64 strips of 4 (16 x 16 rows)
     static constexpr int RatioNT = 64, RatioMAXX = 2, KconvNT = 128, GzNT = 64, GzMAXX = 2;
     static constexpr int Kconv2NT = 128, Kconv2VK = 8, Kconv2MAXC = 6, Kconv2WideNT = 0, Kconv2WideMAXC = 0;
@@ -383,7 +380,7 @@ cudaError_t backward_launch(const Geo& g, const BwdPlan& p, const T* x, const T*
         P.x = x; P.t1 = t1; P.z = z; P.gout = gout; P.h = h; P.bias = bias;
         P.gnum = gnum; P.gden = gden; P.gz = gz;
         P.C = g.G; P.D = g.D; P.H = g.H; P.W = g.W; P.t = p.ratio; P.eps = g.eps; P.relu = g.relu;
-        auto kern = ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, VEC, WQ, packed_kconv<KD, KH, KW>()>;
+        auto kern = ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, VEC, WQ, packed_kconv<KD, KH, KW>() ? kRatioPairs : kRatioPlanar>;
         NDC_CUDA_TRY(set_smem(kern, p.smem_ratio));
         kern<<<(unsigned)p.n_ratio, S::RatioNT, p.smem_ratio, st>>>(P);
         launched();
@@ -536,16 +533,112 @@ cudaError_t backward(const Geo& g, const BwdPlan& p, const T* x, const T* z, con
     return backward_image<T, 3>(g, p, x, z, t1, h, bias, gout, gx, gz, gh, gb, ws, dtype, st);
 }
 
-// Narrowest forward CTA (threads) that still covers a 3x3x3 volume with as few bands as the
-// 256-thread one; 256 if none does.
-inline int fwd_small_class(const Geo& g) {
+// ---------------------------------------------------------------- two-launch forward (3x3x3)
+// t1 = K(relu(z + b)) by ksrc_kernel, then out by ratio_kernel<kRatioForward>.  Measured against
+// the fused fwd_kernel on every stage geometry of the 3-D networks (64^3 x 64 channels ... 8^3 x
+// 512, 128^3) it is 17-29 % faster: no row of t1 is computed twice, the K pass is packed, and
+// both launches run four or more small CTAs per multiprocessor.  The price is traffic: t1 and z
+// are read once more (15 instead of 10 tensor units), which this arithmetic-bound path can pay.
+template <int NT_, int MINB_> struct KsrcShape { static constexpr int NT = NT_, MAXZP = 3, MINB = MINB_; };
+
+template <int KD, int KH, int KW, typename S>
+inline bool plan_ksrc(int D, int H, int W, long long BC, Tiling& t, size_t& smem_bytes) {
+    constexpr int PH = KH / 2;
+    if ((long long)D * H * W >= (1LL << 29) || W > 256) return false;
+    t.NQ = (W + 3) / 4;
+    t.pitch = row_pitch(W);
+    const int NS8 = (t.NQ + 1) / 2;
+    int TH = std::min(H, (S::NT / 2) / NS8);                           // one strip per thread pair
+    TH = std::min(TH, S::NT * S::MAXZP / (2 * t.NQ) - 2 * PH);         // source prefetch registers
+    auto bytes = [&](int th) {
+        Tiling q = t; q.TH = th;
+        return (size_t)KsrcSmem<KD, KH, KW>(q).total_floats * sizeof(float);
+    };
+    const size_t target = (kSmemMax - 8 * 1024) / S::MINB;
+    while (TH > 1 && bytes(TH) > target) --TH;
+    if (TH < 1 || bytes(TH) > target) return false;
+    t.nth = (H + TH - 1) / TH;
+    t.TH = (H + t.nth - 1) / t.nth;
+    plan_depth(KD, D, BC * t.nth, 6, t, S::MINB);
+    smem_bytes = bytes(t.TH);
+    return true;
+}
+
+template <typename T, int KD, int KH, int KW, typename S>
+cudaError_t launch_ksrc(const KsrcParams& P, size_t smem_bytes, long long BC, bool vec, cudaStream_t st) {
+    const long long grid = BC * P.t.ndc * P.t.nth;
+    if (grid > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    auto go = [&](auto kern) -> cudaError_t {
+        NDC_CUDA_TRY(set_smem(kern, smem_bytes));
+        kern<<<(unsigned)grid, S::NT, smem_bytes, st>>>(P);
+        launched();
+        return cudaSuccess;
+    };
+    if (vec && P.W == 64) return go(ksrc_kernel<T, KD, KH, KW, S::NT, S::MAXZP, S::MINB, true, 16>);
+    if (vec && P.W == 128) return go(ksrc_kernel<T, KD, KH, KW, S::NT, S::MAXZP, S::MINB, true, 32>);
+    return vec ? go(ksrc_kernel<T, KD, KH, KW, S::NT, S::MAXZP, S::MINB, true, 0>)
+               : go(ksrc_kernel<T, KD, KH, KW, S::NT, S::MAXZP, S::MINB, false, 0>);
+}
+
+template <typename T, int KD, int KH, int KW, typename S>
+cudaError_t launch_ratio_forward(const RatioParams& P, size_t smem_bytes, long long n_ctas, bool vec,
+                                 cudaStream_t st) {
+    if (n_ctas > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    auto go = [&](auto kern) -> cudaError_t {
+        NDC_CUDA_TRY(set_smem(kern, smem_bytes));
+        kern<<<(unsigned)n_ctas, S::RatioNT, smem_bytes, st>>>(P);
+        launched();
+        return cudaSuccess;
+    };
+    if (vec && P.W == 64) return go(ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, true, 16, kRatioForward>);
+    if (vec && P.W == 128) return go(ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, true, 32, kRatioForward>);
+    return vec ? go(ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, true, 0, kRatioForward>)
+               : go(ratio_kernel<T, KD, KH, KW, S::RatioNT, S::RatioMAXX, false, 0, kRatioForward>);
+}
+
+template <typename T>
+cudaError_t forward_split(const Geo& g, const T* x, const T* z, const float* h, const float* bias,
+                          T* out, T* t1, int dtype, cudaStream_t st, bool& handled) {
+    constexpr int KD = 3, KH = 3, KW = 3;
     const long long BC = (long long)g.B * g.G;
-    Tiling t0, t; size_t smem;
-    if (!plan_fwd<3, 3, 3>(g.D, g.H, g.W, BC, t0, smem)) return 256;
-    if (plan_fwd<3, 3, 3, FwdSmall<32>>(g.D, g.H, g.W, BC, t, smem) && t.nth == t0.nth) return 32;
-    if (plan_fwd<3, 3, 3, FwdSmall<96>>(g.D, g.H, g.W, BC, t, smem) && t.nth == t0.nth) return 96;
-    if (plan_fwd<3, 3, 3, FwdSmall<160>>(g.D, g.H, g.W, BC, t, smem) && t.nth == t0.nth) return 160;
-    return 256;
+    const bool vec = g.W % 4 == 0 && aligned_for_vec(x, dtype) && aligned_for_vec(z, dtype) &&
+                     aligned_for_vec(out, dtype) && aligned_for_vec(t1, dtype);
+    handled = false;
+    // ---- K: the narrowest CTA that covers the volume with as few bands as the widest
+    KsrcParams K;
+    K.z = z; K.h = h; K.bias = bias; K.t1 = t1;
+    K.C = g.G; K.D = g.D; K.H = g.H; K.W = g.W; K.relu = g.relu;
+    Tiling t0, tk; size_t sm0 = 0, smk = 0;
+    typedef KsrcShape<128, 3> K128; typedef KsrcShape<64, 6> K64; typedef KsrcShape<32, 12> K32;
+    if (!plan_ksrc<KD, KH, KW, K128>(g.D, g.H, g.W, BC, t0, sm0)) return cudaSuccess;
+    // ---- A: the same classes as the backward's ratio kernel
+    RatioParams R;
+    R.x = x; R.t1 = t1; R.z = z; R.gout = nullptr; R.h = h; R.bias = bias;
+    R.gnum = nullptr; R.gden = nullptr; R.gz = out;
+    R.C = g.G; R.D = g.D; R.H = g.H; R.W = g.W; R.eps = g.eps; R.relu = g.relu;
+    Tiling r0; size_t smr0 = 0;
+    if (!plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, BwdBands::RatioNT, BwdBands::RatioMAXX, 0, 0,
+                               56 * 1024, 512 / BwdBands::RatioNT, r0, smr0))
+        return cudaSuccess;
+    handled = true;
+    if (plan_ksrc<KD, KH, KW, K32>(g.D, g.H, g.W, BC, tk, smk) && tk.nth == t0.nth) {
+        K.t = tk; NDC_CUDA_TRY((launch_ksrc<T, KD, KH, KW, K32>(K, smk, BC, vec, st)));
+    } else if (plan_ksrc<KD, KH, KW, K64>(g.D, g.H, g.W, BC, tk, smk) && tk.nth == t0.nth) {
+        K.t = tk; NDC_CUDA_TRY((launch_ksrc<T, KD, KH, KW, K64>(K, smk, BC, vec, st)));
+    } else {
+        K.t = t0; NDC_CUDA_TRY((launch_ksrc<T, KD, KH, KW, K128>(K, sm0, BC, vec, st)));
+    }
+    Tiling tr; size_t smr = 0;
+    if (plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, BwdSmall8::RatioNT, BwdSmall8::RatioMAXX, 0, 0,
+                              56 * 1024, 512 / BwdSmall8::RatioNT, tr, smr) && tr.nth == r0.nth) {
+        R.t = tr; NDC_CUDA_TRY((launch_ratio_forward<T, KD, KH, KW, BwdSmall8>(R, smr, BC * tr.ndc * tr.nth, vec, st)));
+    } else if (plan_ring<KD, KH, KW>(g.D, g.H, g.W, BC, 2, BwdSmall16::RatioNT, BwdSmall16::RatioMAXX, 0, 0,
+                                     56 * 1024, 512 / BwdSmall16::RatioNT, tr, smr) && tr.nth == r0.nth) {
+        R.t = tr; NDC_CUDA_TRY((launch_ratio_forward<T, KD, KH, KW, BwdSmall16>(R, smr, BC * tr.ndc * tr.nth, vec, st)));
+    } else {
+        R.t = r0; NDC_CUDA_TRY((launch_ratio_forward<T, KD, KH, KW, BwdBands>(R, smr0, BC * r0.ndc * r0.nth, vec, st)));
+    }
+    return cudaGetLastError();
 }
 
 // Forward plan of a K x K image batch: the row kernels of its class, else the band kernels.
@@ -570,7 +663,10 @@ inline bool covers(const Geo& g) {
     const long long BC = (long long)g.B * g.G;
     BwdPlan bp;
     if (!plan_bwd_any(g, bp)) return false;
-    if (g.kD == 3) return plan_fwd<3, 3, 3>(g.D, g.H, g.W, BC, t, smem);
+    if (g.kD == 3)
+        return plan_ksrc<3, 3, 3, KsrcShape<128, 3>>(g.D, g.H, g.W, BC, t, smem) &&
+               plan_ring<3, 3, 3>(g.D, g.H, g.W, BC, 2, BwdBands::RatioNT, BwdBands::RatioMAXX, 0, 0,
+                                  56 * 1024, 512 / BwdBands::RatioNT, t, smem);
     if (g.kH == 5) return plan_fwd_image<5>(g);
     return plan_fwd_image<3>(g);
 }
@@ -596,14 +692,8 @@ cudaError_t forward(const Geo& g, const T* x, const T* z, const float* h, const 
                     T* out, T* t1, int dtype, cudaStream_t st, bool& handled) {
     handled = false;
     if (g.m != 1 || g.sc != SCH) return cudaSuccess;
-    if (g.kD == 3 && g.kH == 3 && g.kW == 3) {
-        switch (fwd_small_class(g)) {
-            case 32: return forward_shape<T, 3, 3, 3, FwdSmall<32>>(g, x, z, h, bias, out, t1, dtype, st, handled);
-            case 96: return forward_shape<T, 3, 3, 3, FwdSmall<96>>(g, x, z, h, bias, out, t1, dtype, st, handled);
-            case 160: return forward_shape<T, 3, 3, 3, FwdSmall<160>>(g, x, z, h, bias, out, t1, dtype, st, handled);
-            default: return forward_shape<T, 3, 3, 3>(g, x, z, h, bias, out, t1, dtype, st, handled);
-        }
-    }
+    if (g.kD == 3 && g.kH == 3 && g.kW == 3)
+        return forward_split<T>(g, x, z, h, bias, out, t1, dtype, st, handled);
     if (g.kD == 1 && g.kH == 5 && g.kW == 5)
         return forward_image<T, 5>(g, x, z, h, bias, out, t1, dtype, st, handled);
     if (g.kD == 1 && g.kH == 3 && g.kW == 3)
