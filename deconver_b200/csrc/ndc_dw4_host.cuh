@@ -180,6 +180,24 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
     while (TH > 1 && (bytes(TH) > smem_target || (TH + 2 * PH) * t.pitch > 65535)) --TH;
     if (TH < 1 || bytes(TH) > kSmemMax) return false;
     t.nth = (H + TH - 1) / TH;
+    if (KD > 1) {
+        // A plane's strips are worked off in rounds of `nt` (one strip per thread): prefer the
+        // band count whose bands fill their rounds (13 rows of 16 strips on 128 threads waste
+        // 3/8 of every second round, 8 rows none), against the two halo rows a band reloads.
+        double best = -1.0;
+        int best_nth = t.nth;
+        for (int nth = t.nth; nth <= std::min(H, 4 * t.nth); ++nth) {
+            const int th = (H + nth - 1) / nth;
+            if ((nth - 1) * th >= H) continue;                     // an empty last band
+            const int last = H - (nth - 1) * th;
+            const long long rounds = (long long)(nth - 1) * (((long long)th * t.NQ + nt - 1) / nt) +
+                                     ((long long)last * t.NQ + nt - 1) / nt;
+            const double fill = (double)H * t.NQ / ((double)rounds * nt);
+            const double score = fill / (1.0 + 0.3 * PH * nth / H);
+            if (score > best * 1.001) { best = score; best_nth = nth; }
+        }
+        t.nth = best_nth;
+    }
     t.TH = (H + t.nth - 1) / t.nth;
     plan_depth(KD, D, BC * t.nth, 6, t, ctas_per_sm);
     smem_bytes = bytes(t.TH);
