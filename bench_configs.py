@@ -94,6 +94,10 @@ def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, dept
     if use_b200 and own_norm:   # the same operator on this library's kernels
         norm = deconver_b200.InstanceNorm3d if spatial_dims == 3 else deconver_b200.InstanceNorm2d
     dm.Deconv = deconver_b200.Deconv if use_b200 else RefDeconv
+    import deconver.layers.mlp as mlp_module
+    ref_linear = dm.Linear
+    if use_b200 and own_norm:   # the reference's Linear with this library's bias kernels
+        dm.Linear = mlp_module.Linear = deconver_b200.Linear
     try:
         torch.manual_seed(0)
         model = dc.Deconver(
@@ -104,6 +108,7 @@ def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, dept
         )
     finally:
         dm.Deconv = RefDeconv
+        dm.Linear = mlp_module.Linear = ref_linear
     return model, (deconver_b200.Deconv if use_b200 else RefDeconv)
 
 

@@ -3,7 +3,7 @@
 The library is built in-tree (next to this file) so that it travels with the source tree.
 nvcc cross-compiles without a GPU.  The tiled kernels are compiled as six translation units
 (forward / backward of volumes / backward of images, each for float32 and bfloat16) next to the
-ABI unit and the instance-norm unit, in parallel, then linked.  Run as `python -m deconver_b200._build [--force]`.
+ABI unit and the instance-norm and bias units, in parallel, then linked.  Run as `python -m deconver_b200._build [--force]`.
 """
 
 import os
@@ -26,7 +26,7 @@ NVCC_FLAGS = [
 ]
 
 # (object name, source, extra defines)
-UNITS = [("abi", "ndc_abi.cu", []), ("inorm", "ndc_inorm.cu", [])] + [
+UNITS = [("abi", "ndc_abi.cu", []), ("inorm", "ndc_inorm.cu", []), ("bias", "ndc_bias.cu", [])] + [
     ("dw4_p%d_t%d" % (part, t), "ndc_dw4_inst.cu", ["-DNDC_DW4_PART=%d" % part, "-DNDC_DW4_T=%d" % t])
     for part in (1, 2, 0) for t in (0, 1)   # the longest units first
 ]

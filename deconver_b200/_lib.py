@@ -20,7 +20,8 @@ SYMBOLS = (
     "ndc_version", "ndc_last_error", "ndc_status_string", "ndc_launch_count", "ndc_query",
     "ndc_fwd", "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_bwd_static", "ndc_gconv",
     "ndc_probe_fp32_fma", "ndc_inorm_workspace_bytes", "ndc_inorm_last_error", "ndc_inorm_fwd",
-    "ndc_inorm_bwd",
+    "ndc_inorm_bwd", "ndc_bias_grad_workspace_bytes", "ndc_bias_last_error", "ndc_bias_add",
+    "ndc_bias_grad",
 )
 
 
@@ -88,6 +89,14 @@ def load():
     lib.ndc_inorm_bwd.restype = ctypes.c_int
     lib.ndc_inorm_bwd.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp,
                                   vp, fp, fp, vp, fp, fp, vp, ctypes.c_size_t, vp]
+    lib.ndc_bias_grad_workspace_bytes.restype = ctypes.c_size_t
+    lib.ndc_bias_grad_workspace_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32]
+    lib.ndc_bias_last_error.restype = ctypes.c_char_p
+    lib.ndc_bias_add.restype = ctypes.c_int
+    lib.ndc_bias_add.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp, fp, vp]
+    lib.ndc_bias_grad.restype = ctypes.c_int
+    lib.ndc_bias_grad.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp, fp,
+                                  vp, ctypes.c_size_t, vp]
     _lib = lib
     return lib
 

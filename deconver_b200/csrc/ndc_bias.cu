@@ -1,0 +1,164 @@
+// Bias of the channels-first linear layer: y[b, c, :] += bias[c], and its gradient
+// gbias[c] = sum over samples and positions of gy[b, c, :].
+//
+// The 1x1 projection itself is a library GEMM; what the library adds around it, a broadcast add
+// that is not vectorised and a reduction with one block per output, is slow at the small per-GPU
+// batches of a batch-sharded training step.  Both are plain HBM-bound passes here: every
+// (sample, channel) slab is split over as many CTAs as fill the GPU, 16-byte accesses, sums in a
+// fixed order (no atomics).
+#include <cstdarg>
+#include <cstdio>
+
+#include "ndc_b200.h"
+#include "ndc_common.cuh"
+#include "ndc_slab.cuh"
+
+namespace {
+
+using namespace ndc::slab;
+
+thread_local char g_bias_err[256] = "";
+
+int bias_fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_bias_err, sizeof(g_bias_err), fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kNT) bias_add_kernel(T* __restrict__ y, long long sp, int channels,
+                                                       int nsplit, const float* __restrict__ bias) {
+    const long long slab = blockIdx.x / nsplit;
+    const int part = blockIdx.x % nsplit;
+    T* ys = y + slab * sp;
+    const float b = bias[slab % channels];
+    long long begin, end;
+    part_range(sp, nsplit, part, Vec16<T>::N, begin, end);
+    constexpr int N = Vec16<T>::N;
+    if (VEC) {
+        for (long long i = begin + (long long)threadIdx.x * N; i < end; i += (long long)kNT * N) {
+            float v[N];
+            Vec16<T>::unpack(*reinterpret_cast<const typename Vec16<T>::raw*>(ys + i), v);
+#pragma unroll
+            for (int j = 0; j < N; ++j) v[j] += b;
+            *reinterpret_cast<typename Vec16<T>::raw*>(ys + i) = Vec16<T>::pack(v);
+        }
+    } else {
+        for (long long i = begin + threadIdx.x; i < end; i += kNT)
+            ys[i] = ndc::from_f32<T>(ndc::to_f32(ys[i]) + b);
+    }
+}
+
+// partial[slab * nsplit + part] = sum of the part
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kNT) bias_grad_partial_kernel(const T* __restrict__ gy, long long sp,
+                                                                int nsplit, float* __restrict__ partial) {
+    __shared__ float scratch[2 * kNT / 32];
+    const long long slab = blockIdx.x / nsplit;
+    const int part = blockIdx.x % nsplit;
+    const T* gs = gy + slab * sp;
+    long long begin, end;
+    part_range(sp, nsplit, part, Vec16<T>::N, begin, end);
+    constexpr int N = Vec16<T>::N;
+    float s1 = 0.0f, s2 = 0.0f;     // two interleaved sums: shorter dependency chains
+    if (VEC) {
+        for (long long i = begin + (long long)threadIdx.x * N; i < end; i += (long long)kNT * N) {
+            float v[N];
+            Vec16<T>::unpack(__ldg(reinterpret_cast<const typename Vec16<T>::raw*>(gs + i)), v);
+#pragma unroll
+            for (int j = 0; j < N; j += 2) { s1 += v[j]; s2 += v[j + 1]; }
+        }
+    } else {
+        for (long long i = begin + threadIdx.x; i < end; i += kNT) s1 += ndc::to_f32(gs[i]);
+    }
+    cta_sum2(s1, s2, scratch);
+    if (threadIdx.x == 0) partial[slab * nsplit + part] = s1 + s2;
+}
+
+__global__ void bias_grad_final_kernel(const float* __restrict__ partial, int batch, int channels, int nsplit,
+                                       float* __restrict__ gbias) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    float s = 0.0f;
+    for (int b = 0; b < batch; ++b)
+        for (int i = 0; i < nsplit; ++i) s += partial[((long long)b * channels + c) * nsplit + i];
+    gbias[c] = s;
+}
+
+int check(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype) {
+    if (batch <= 0 || channels <= 0 || spatial <= 0)
+        return bias_fail(NDC_ERR_INVALID, "bias: batch, channels and spatial size must be positive");
+    if (dtype != NDC_F32 && dtype != NDC_BF16)
+        return bias_fail(NDC_ERR_INVALID, "bias: dtype must be NDC_F32 or NDC_BF16");
+    if ((long long)batch * channels * kMaxSplit > 0x7fffffffLL)
+        return bias_fail(NDC_ERR_UNSUPPORTED, "bias: batch * channels is too large");
+    return NDC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* ndc_bias_last_error(void) { return g_bias_err; }
+
+size_t ndc_bias_grad_workspace_bytes(int32_t batch, int32_t channels) {
+    if (batch <= 0 || channels <= 0) return 0;
+    return (size_t)batch * channels * kMaxSplit * sizeof(float);
+}
+
+int ndc_bias_add(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, void* y,
+                 const float* bias, void* stream) {
+    if (!y || !bias) return bias_fail(NDC_ERR_INVALID, "bias add: y and bias must not be NULL");
+    int st = check(batch, channels, spatial, dtype);
+    if (st != NDC_OK) return st;
+    const long long slabs = (long long)batch * channels;
+    const int nsplit = choose_split(slabs, spatial);
+    const bool vec = spatial % (dtype == NDC_BF16 ? 8 : 4) == 0 && ((uintptr_t)y % 16) == 0;
+    const unsigned grid = (unsigned)(slabs * nsplit);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == NDC_F32) {
+        if (vec) bias_add_kernel<float, true><<<grid, kNT, 0, s>>>((float*)y, spatial, channels, nsplit, bias);
+        else bias_add_kernel<float, false><<<grid, kNT, 0, s>>>((float*)y, spatial, channels, nsplit, bias);
+    } else {
+        typedef __nv_bfloat16 bf16;
+        if (vec) bias_add_kernel<bf16, true><<<grid, kNT, 0, s>>>((bf16*)y, spatial, channels, nsplit, bias);
+        else bias_add_kernel<bf16, false><<<grid, kNT, 0, s>>>((bf16*)y, spatial, channels, nsplit, bias);
+    }
+    ndc::launched();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return bias_fail(NDC_ERR_CUDA, "bias add: %s", cudaGetErrorString(e));
+    return NDC_OK;
+}
+
+int ndc_bias_grad(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, const void* gy,
+                  float* gbias, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!gy || !gbias) return bias_fail(NDC_ERR_INVALID, "bias gradient: gy and gbias must not be NULL");
+    int st = check(batch, channels, spatial, dtype);
+    if (st != NDC_OK) return st;
+    if (!workspace || workspace_bytes < ndc_bias_grad_workspace_bytes(batch, channels))
+        return bias_fail(NDC_ERR_WORKSPACE, "bias gradient: workspace of %zu bytes needed",
+                         ndc_bias_grad_workspace_bytes(batch, channels));
+    const long long slabs = (long long)batch * channels;
+    const int nsplit = choose_split(slabs, spatial);
+    const bool vec = spatial % (dtype == NDC_BF16 ? 8 : 4) == 0 && ((uintptr_t)gy % 16) == 0;
+    const unsigned grid = (unsigned)(slabs * nsplit);
+    cudaStream_t s = (cudaStream_t)stream;
+    float* partial = (float*)workspace;
+    if (dtype == NDC_F32) {
+        if (vec) bias_grad_partial_kernel<float, true><<<grid, kNT, 0, s>>>((const float*)gy, spatial, nsplit, partial);
+        else bias_grad_partial_kernel<float, false><<<grid, kNT, 0, s>>>((const float*)gy, spatial, nsplit, partial);
+    } else {
+        typedef __nv_bfloat16 bf16;
+        if (vec) bias_grad_partial_kernel<bf16, true><<<grid, kNT, 0, s>>>((const bf16*)gy, spatial, nsplit, partial);
+        else bias_grad_partial_kernel<bf16, false><<<grid, kNT, 0, s>>>((const bf16*)gy, spatial, nsplit, partial);
+    }
+    bias_grad_final_kernel<<<(channels + 127) / 128, 128, 0, s>>>(partial, batch, channels, nsplit, gbias);
+    ndc::launched(2);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return bias_fail(NDC_ERR_CUDA, "bias gradient: %s", cudaGetErrorString(e));
+    return NDC_OK;
+}
+
+}  // extern "C"

@@ -198,6 +198,23 @@ int ndc_inorm_bwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtyp
                   void *stream);
 
 /*
+ * Bias of the channels-first linear layer (`Linear`, deconver/layers/linear.py:34-58: a 1x1
+ * `nn.Conv1d` over the flattened spatial axes).  The product itself stays a library GEMM; these
+ * two calls replace what the library wraps around it:
+ *     ndc_bias_add    y[b, c, :] += bias[c]            in place, y of dtype `dtype`
+ *     ndc_bias_grad   gbias[c] = sum_{b, p} gy[b, c, p]  float32, overwritten, fixed order
+ * `spatial` = positions per (sample, channel).  ndc_bias_grad needs
+ * ndc_bias_grad_workspace_bytes(batch, channels) bytes of device scratch.  Errors: status code,
+ * message from ndc_bias_last_error().
+ */
+size_t ndc_bias_grad_workspace_bytes(int32_t batch, int32_t channels);
+const char *ndc_bias_last_error(void);
+int ndc_bias_add(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, void *y,
+                 const float *bias, void *stream);
+int ndc_bias_grad(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, const void *gy,
+                  float *gbias, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Measurement aid; no counterpart in the reference project.  Launches one kernel of
  * register-only fused multiply-add chains (4 blocks of 256 threads per multiprocessor, 8
  * independent chains per thread, iters x 64 instructions per thread) on `stream`: plain

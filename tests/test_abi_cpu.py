@@ -159,3 +159,10 @@ def test_instance_norm_and_probe_entry_points_validate_without_a_gpu(lib):
                              None) == 1
     assert lib.ndc_probe_fp32_fma(0, 0, None, 0, None, None) == 1
     assert b"iters" in lib.ndc_last_error()
+
+
+def test_bias_entry_points_validate_without_a_gpu(lib):
+    assert lib.ndc_bias_grad_workspace_bytes(2, 64) == 2 * 64 * 64 * 4
+    assert lib.ndc_bias_add(2, 64, 4096, 0, None, None, None) == 1
+    assert b"NULL" in lib.ndc_bias_last_error()
+    assert lib.ndc_bias_grad(2, 64, 4096, 0, None, None, None, 0, None) == 1

@@ -86,3 +86,38 @@ def test_module_matches_torch_module_and_is_reproducible(dev):
         dcb.instance_norm(torch.randn(1, 2, 4))
     with pytest.raises(NotImplementedError):
         dcb.InstanceNorm1d(4, track_running_stats=True)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 2e-2)], ids=["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(2, 64, 256, (32, 32, 32)), (3, 5, 7, (9, 11)), (1, 16, 8, (4100,))],
+                         ids=["volume", "odd", "row"])
+def test_linear_matches_conv1d(dev, dtype, tol, shape):
+    """`deconver_b200.Linear` (library product + this library's bias add and bias gradient)
+    against the plain `nn.Conv1d` form of the reference's `Linear` (`layers/linear.py:34-58`),
+    evaluated in float64."""
+    B, Ci, Co, S = shape
+    torch.manual_seed(Ci + Co)
+    mine = dcb.Linear(Ci, Co).to(device=dev, dtype=dtype)
+    ref = torch.nn.Conv1d(Ci, Co, 1).double()
+    ref.load_state_dict({k.replace("linear.", ""): v.double().cpu() for k, v in mine.state_dict().items()})
+    assert sorted(mine.state_dict()) == ["linear.bias", "linear.weight"]
+    x = torch.randn(B, Ci, *S).to(dtype)
+    g = torch.randn(B, Co, *S).to(dtype)
+    xd = x.to(dev).requires_grad_(True)
+    old_flags = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False        # the product is a library call: float32, not TF32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        y = mine(xd)
+        y.backward(g.to(dev))
+        torch.cuda.synchronize()
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = old_flags
+    x64 = x.double().flatten(2).requires_grad_(True)
+    y64 = ref(x64)
+    y64.backward(g.double().flatten(2))
+    assert y.shape == (B, Co, *S) and y.dtype == dtype
+    assert max_norm_error(y.detach().float().cpu().flatten(2).numpy(), y64.detach().numpy()) < tol
+    assert max_norm_error(mine.linear.bias.grad.float().cpu().numpy(), ref.bias.grad.numpy()) < max(tol, 1e-4)
+    assert max_norm_error(mine.linear.weight.grad.float().cpu().numpy(), ref.weight.grad.numpy()) < max(tol, 1e-4)
+    assert max_norm_error(xd.grad.float().cpu().flatten(2).numpy(), x64.grad.numpy()) < max(tol, 1e-4)

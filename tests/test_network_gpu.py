@@ -46,15 +46,20 @@ def reference():
 
 
 def _network(reference, layer_cls, dev, norm=None):
+    """`norm` given: the network also gets this library's InstanceNorm3d and Linear."""
     dc, module, _ = reference
-    original = module.Deconv
+    import deconver.layers.mlp as mlp_module
+    original, linear = module.Deconv, module.Linear
     module.Deconv = layer_cls
+    if norm is not None:
+        module.Linear = mlp_module.Linear = dcb.Linear
     try:
         torch.manual_seed(0)
         kwargs = dict(NETWORK, norm=norm) if norm is not None else NETWORK
         return dc.Deconver(**kwargs).to(dev).eval()
     finally:
         module.Deconv = original
+        module.Linear = mlp_module.Linear = linear
 
 
 def _errors(a, b):
@@ -64,7 +69,8 @@ def _errors(a, b):
 
 @pytest.mark.parametrize("own_norm", [False, True], ids=["layer", "layer_and_norm"])
 def test_network_on_this_layer_is_as_close_to_float64_as_the_original(reference, own_norm):
-    """`own_norm`: the network is also given this library's InstanceNorm3d as its `norm` class."""
+    """`own_norm`: the network is also given this library's InstanceNorm3d as its `norm` class
+    and this library's Linear for its 1x1 projections."""
     assert torch.cuda.is_available(), "GPU tests need a CUDA device"
     dcb.load_library()
     dev = torch.device("cuda:0")
@@ -72,6 +78,8 @@ def test_network_on_this_layer_is_as_close_to_float64_as_the_original(reference,
     old = _network(reference, ReferenceDeconv, dev)
     new = _network(reference, dcb.Deconv, dev, norm=dcb.InstanceNorm3d if own_norm else None)
     assert any(isinstance(m, dcb.InstanceNorm3d) for m in new.modules()) == own_norm
+    mixers = [m for m in new.modules() if type(m).__name__ == "DeconvMixer"]
+    assert mixers and all((type(m.out_proj) is dcb.Linear) == own_norm for m in mixers)
     assert any(isinstance(m, dcb.Deconv) for m in new.modules())
     assert not any(isinstance(m, ReferenceDeconv) for m in new.modules())
     assert list(old.state_dict()) == list(new.state_dict())
