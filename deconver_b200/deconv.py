@@ -17,7 +17,7 @@ import torch.nn.functional as F
 from torch import Tensor, nn
 
 from .functional import deconv_update, kernels_apply
-from .linear import Linear
+from .linear import Linear, conv1x1
 
 __all__ = ["Initializer", "Deconv", "NDC"]
 
@@ -138,7 +138,7 @@ class Deconv(nn.Module):
         h = F.relu(self.init.h0)  # batch-invariant
         # the source enters the update pre-ReLU and pre-bias: the kernels apply both on load
         projection = self.init.linear.linear
-        s = F.conv1d(x.flatten(2), projection.weight, None)
+        s = conv1x1(x.flatten(2), projection.weight)
         s = s.view(x.shape[0], -1, *x.shape[2:])
         bias = projection.bias
         rectify = True

@@ -5,8 +5,8 @@ spatial axes, so the parameters are named `linear.weight` / `linear.bias` and ch
 both ways.  The product is the library's convolution; on CUDA the bias is added (and its gradient
 reduced) by this library's own kernels (`csrc/ndc_bias.cu`): the library's broadcast add is not
 vectorised and its reduction uses one block per output channel, which shows at the small per-GPU
-batches of a batch-sharded training step.  CPU tensors and other dtypes take the plain
-`nn.Conv1d` with its bias.
+batches of a batch-sharded training step.  For bfloat16 the weight gradient is a split batched
+GEMM (`_weight_grad`).  CPU tensors and other dtypes take the plain `nn.Conv1d` with its bias.
 """
 
 from typing import Optional
@@ -61,6 +61,63 @@ class _BiasAdd(torch.autograd.Function):
         return gy, gbias
 
 
+def _weight_grad(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """``dW[o, c] = sum_{b, p} gy[b, o, p] * x[b, c, p]`` of a 1x1 convolution, ``(Co, Ci)``.
+
+    This is a GEMM with a tiny output and a huge inner dimension (every position of every
+    sample).  At the small per-GPU batches of a batch-sharded training step the library's
+    convolution backward takes 3-4x the time the two reads need (0.31 ms against 0.09 ms for
+    bfloat16 tensors of 2 x 256 x 64^3 and 2 x 64 x 64^3).  Here the positions of each sample
+    are cut into S slices and ONE strided batched GEMM (library) multiplies all slices, with
+    float32 partial products that are then added in a fixed order; no operand is copied: the
+    slices are views of the tensors as they lie.  Large batches, float32 and CPU tensors keep
+    the library's own weight gradient, which is the faster one there.
+    """
+    B, Co, N = gy.shape
+    Ci = x.shape[1]
+    S = 1
+    while S * 2 * B <= 32 and N % (S * 2 * 8) == 0 and N // (S * 2) >= 2048:
+        S *= 2
+    if gy.dtype != torch.bfloat16 or not gy.is_cuda or B > 8 or S == 1:
+        return torch.nn.grad.conv1d_weight(x, (Co, Ci, 1), gy)[:, :, 0]
+    L = N // S
+    parts = []
+    for b in range(B):
+        a = gy[b].view(Co, S, L).transpose(0, 1)          # (S, Co, L), strides (L, N, 1)
+        c = x[b].view(Ci, S, L).permute(1, 2, 0)          # (S, L, Ci), strides (L, 1, N)
+        parts.append(torch.bmm(a, c, out_dtype=torch.float32))
+    return torch.cat(parts).sum(0)
+
+
+class Conv1x1(torch.autograd.Function):
+    """``y = W x`` over the channel axis of a contiguous ``(B, Ci, N)`` tensor, no bias: the
+    library's convolution forward and input gradient, and `_weight_grad` for the weight."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return F.conv1d(x, weight, None)
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, gy):
+        x, weight = ctx.saved_tensors
+        gy = gy.contiguous()
+        gx = gw = None
+        if ctx.needs_input_grad[0]:
+            gx = F.conv1d(gy, weight.transpose(0, 1).contiguous(), None)     # W^T gy
+        if ctx.needs_input_grad[1]:
+            gw = _weight_grad(gy, x).unsqueeze(-1).to(weight.dtype)
+        return gx, gw
+
+
+def conv1x1(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """1x1 convolution of a ``(B, Ci, N)`` tensor with ``weight`` ``(Co, Ci, 1)``, no bias."""
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3:
+        return Conv1x1.apply(x.contiguous(), weight)
+    return F.conv1d(x, weight, None)
+
+
 class Linear(nn.Module):
     def __init__(self, in_channels: int, out_channels: int, bias: bool = True,
                  device: Optional[torch.device] = None, dtype: Optional[torch.dtype] = None):
@@ -73,8 +130,10 @@ class Linear(nn.Module):
         shape = x.shape
         flat = self.flatten(x)
         bias = self.linear.bias
-        if bias is None or not flat.is_cuda or flat.dtype not in _DTYPES or flat.dim() != 3:
+        if not flat.is_cuda or flat.dtype not in _DTYPES or flat.dim() != 3:
             y = self.linear(flat)
+        elif bias is None:
+            y = conv1x1(flat, self.linear.weight)
         else:
-            y = _BiasAdd.apply(F.conv1d(flat, self.linear.weight, None), bias)
+            y = _BiasAdd.apply(conv1x1(flat, self.linear.weight), bias)
         return y.view(shape[0], -1, *shape[2:])
