@@ -141,7 +141,7 @@ cudaError_t forward_shape(const Geo& g, const T* x, const T* z, const float* h, 
 // Kconv2MAXC: 16-byte source chunks a thread copies per plane, at most (bands shrink to fit).
 struct BwdBands {
     static constexpr int RatioNT = 128, RatioMAXX = 2, KconvNT = 192, GzNT = 128, GzMAXX = 4;
-    static constexpr int Kconv2NT = 128, Kconv2VK = 8, Kconv2MAXC = 6, Kconv2WideNT = 256, Kconv2WideMAXC = 5;
+    static constexpr int Kconv2NT = 128, Kconv2VK = 8, Kconv2MAXC = 6, Kconv2WideNT = 256, Kconv2WideMAXC = 6;
 };
 // Rows: one-row planes of NQ 4-voxel strips (2-D images run as volumes, see FwdRows).
 template <int NQ_> struct BwdRows {
