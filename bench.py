@@ -18,9 +18,11 @@ input and upstream gradient, host<->device copies inside the timed region.
 (`ReferenceDeconv`, imported from an installation of the reference under `baseline/_ref`;
 the oracle's port of it when that directory is absent) on all host cores.
 
-Two sub-records ride along on the GPU arm when `baseline/_ref` is importable: `train_step`
-(the full 3-D network's training step, global batch 16 split over the ranks, at every N) and
-`triton` (the reference's own Triton kernels on the same GPU and layer, N = 1 only).
+Sub-records ride along on the GPU arm when `baseline/_ref` is importable: `train_step` (the
+full 3-D network's training step, global batch 16 split over the ranks) and `inference` (the
+large 3-D inference configuration, batch 32 split over the ranks) at every N; `triton` (the
+reference's own Triton kernels on the same GPU and layer) and `forward_2d` (the full 2-D
+network's forward) at N = 1 only.
 
 `--profile-case` runs a few update calls on a small case and nothing else: the command the
 ncu summaries under `profiles/` were captured with.
@@ -279,8 +281,9 @@ def measure_fp32_fma_peak(lib, dev):
 
 
 def sub_records(args, world, rank):
-    """`train_step` (every N) and `triton` (N = 1): measured through bench_configs.py's code
-    with the reference's own network around this library's layer."""
+    """`train_step` and `inference` (every N), `triton` and `forward_2d` (N = 1): measured
+    through bench_configs.py's code with the reference's own network around this library's
+    layer, norm and Linear."""
     out = {}
     if args.no_sub_records:
         return out
@@ -293,8 +296,10 @@ def sub_records(args, world, rank):
         why = "baseline/_ref (an installation of the reference) is not present"
     if dc is None:
         out["train_step"] = {"unavailable": why}
+        out["inference"] = {"unavailable": why}
         if world == 1:
             out["triton"] = {"unavailable": why}
+            out["forward_2d"] = {"unavailable": why}
         return out
     try:
         # forward + backward replayed as one CUDA graph; the plain launch sequence beside it
@@ -307,11 +312,23 @@ def sub_records(args, world, rank):
         out["train_step"] = rec
     except Exception as exc:
         out["train_step"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+    try:
+        rec = bench_configs.inference_record(dc)
+        rec["workload"] = ("large 3D Deconver inference, bf16, batch 32 of 4x128^3 split over the "
+                           "ranks, no collective; NDC share of the end-to-end time")
+        out["inference"] = rec
+    except Exception as exc:
+        out["inference"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     if world == 1:
         try:
             out["triton"] = bench_configs.triton_record(dc, "cfg3")
         except Exception as exc:
             out["triton"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
+        try:
+            out["forward_2d"] = {"workload": "full 2D Deconver forward, batch 16x3x256x256",
+                                 "runs": bench_configs.forward2d_records(dc)}
+        except Exception as exc:
+            out["forward_2d"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
     return out
 
 

@@ -215,14 +215,16 @@ def config_1(dc, args):
          b200=dict(ms=gpu_ms, voxels_per_s=vox / gpu_ms * 1e3))
 
 
-def config_2(dc, args):
-    """Full 2-D Deconver forward, batch 16 x 3 x 256 x 256, fp32 and bf16."""
-    dev = torch.device("cuda", 0)
+def forward2d_records(dc, with_reference=True):
+    """Full 2-D Deconver forward, batch 16 x 3 x 256 x 256, fp32 and bf16, on one GPU.  Returns a
+    list of records (this library in both dtypes; the reference's Triton path in fp32)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
     x0 = torch.rand(16, 3, 256, 256, device=dev)
     vox = 16 * 256 * 256
+    out = []
     for dtype in (torch.float32, torch.bfloat16):
         for use_b200 in (True, False):
-            if not use_b200 and dtype != torch.float32:
+            if not use_b200 and (dtype != torch.float32 or not with_reference):
                 continue  # the reference's Triton path is float32 only
             model, cls = build_model(dc, use_b200, 2, 3, 1, (32, 64, 128, 256, 512),
                                      (1, 2, 2, 2, 2), (1, 1, 1, 1), (5, 5))
@@ -238,10 +240,16 @@ def config_2(dc, args):
             clock.reset()
             fwd()
             ndc = clock.total_ms()
-            emit(config=2, impl="b200" if use_b200 else "reference_triton",
-                 dtype=str(dtype).split(".")[-1], ms=ms, voxels_per_s=vox / ms * 1e3,
-                 ndc_layers=len(clock.pairs), ndc_ms=ndc, ndc_share=ndc / ms)
+            out.append(dict(impl="b200" if use_b200 else "reference_triton",
+                            dtype=str(dtype).split(".")[-1], ms=ms, voxels_per_s=vox / ms * 1e3,
+                            ndc_layers=len(clock.pairs), ndc_ms=ndc, ndc_share=ndc / ms))
             del model
+    return out
+
+
+def config_2(dc, args):
+    for rec in forward2d_records(dc):
+        emit(config=2, **rec)
 
 
 def train_step_record(dc, steps=10, graph=False, per_gpu_batch=0):
@@ -339,9 +347,10 @@ def config_4(dc, args):
         dist.destroy_process_group()
 
 
-def config_5(dc, args):
-    """Large 3-D inference, bf16: batch 32 of 4 x 128^3 (relu(N(0,1))), processed in chunks of
-    `--chunk` samples on one GPU; reports the NDC share of the end-to-end time."""
+def inference_record(dc, chunk=4):
+    """Large 3-D inference, bf16: batch 32 of 4 x 128^3 (relu(N(0,1))), batch-sharded over the
+    ranks of the current process group with no collective, processed in chunks of `chunk`
+    samples per GPU; reports the NDC share of the end-to-end time."""
     from deconver_b200.distributed import init_from_env, shard_batch
     import torch.distributed as dist
 
@@ -354,7 +363,7 @@ def config_5(dc, args):
     sl = shard_batch(32, rank, world)
     nb = sl.stop - sl.start
     gen = torch.Generator(device=dev).manual_seed(7 + rank)
-    chunk = min(args.chunk, nb)
+    chunk = min(chunk, nb)
     xs = [torch.relu(torch.randn(chunk, 4, 128, 128, 128, device=dev, generator=gen)).to(torch.bfloat16)
           for _ in range(2)]
 
@@ -371,8 +380,14 @@ def config_5(dc, args):
     clock.reset()
     run()
     ndc = clock.total_ms()
-    emit(config=5, n_gpus=world, batch=32, per_gpu_batch=nb, chunk=chunk, dtype="bfloat16", ms=ms,
-         voxels_per_s=32 * 128 ** 3 / ms * 1e3, ndc_ms_per_rank=ndc, ndc_share=ndc / ms)
+    return dict(n_gpus=world, batch=32, per_gpu_batch=nb, chunk=chunk, dtype="bfloat16", ms=ms,
+                voxels_per_s=32 * 128 ** 3 / ms * 1e3, ndc_ms_per_rank=ndc, ndc_share=ndc / ms)
+
+
+def config_5(dc, args):
+    import torch.distributed as dist
+
+    emit(config=5, **inference_record(dc, args.chunk))
     if dist.is_initialized():
         dist.destroy_process_group()
 
