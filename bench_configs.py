@@ -90,14 +90,19 @@ def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, dept
     import deconver_b200
     from deconver.deconvolution.deconv import Deconv as RefDeconv
 
+    # The network's own convolutions (stem, strided down/up-sampling, 1x1 head) are library
+    # calls; let the library time its algorithms once per shape instead of trusting its
+    # heuristic, which picks a 4.6x slower kernel for the stem at a per-GPU batch of 2.
+    torch.backends.cudnn.benchmark = True
     norm = torch.nn.InstanceNorm3d if spatial_dims == 3 else torch.nn.InstanceNorm2d
     if use_b200 and own_norm:   # the same operator on this library's kernels
         norm = deconver_b200.InstanceNorm3d if spatial_dims == 3 else deconver_b200.InstanceNorm2d
     dm.Deconv = deconver_b200.Deconv if use_b200 else RefDeconv
     import deconver.layers.mlp as mlp_module
-    ref_linear = dm.Linear
-    if use_b200 and own_norm:   # the reference's Linear with this library's bias kernels
+    ref_linear, ref_mlp = dm.Linear, dm.MLP
+    if use_b200 and own_norm:   # the reference's Linear / MLP with this library's bias kernels
         dm.Linear = mlp_module.Linear = deconver_b200.Linear
+        dm.MLP = deconver_b200.MLP
     try:
         torch.manual_seed(0)
         model = dc.Deconver(
@@ -109,6 +114,7 @@ def build_model(dc, use_b200, spatial_dims, in_ch, out_ch, widths, strides, dept
     finally:
         dm.Deconv = RefDeconv
         dm.Linear = mlp_module.Linear = ref_linear
+        dm.MLP = ref_mlp
     return model, (deconver_b200.Deconv if use_b200 else RefDeconv)
 
 
@@ -334,8 +340,8 @@ def train_step_record(dc, steps=10, graph=False, per_gpu_batch=0):
         model(x)
     ndc_fwd = clock.total_ms()
     return dict(n_gpus=world, global_batch=16, per_gpu_batch=nb, dtype="bfloat16",
-                cuda_graph=bool(graph), steps=steps, ms_per_step=ms,
-                voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss.detach()),
+                cuda_graph=bool(graph), cudnn_benchmark=bool(torch.backends.cudnn.benchmark),
+                steps=steps, ms_per_step=ms, voxels_per_s=16 * 64 ** 3 / ms * 1e3, loss=float(loss.detach()),
                 ndc_forward_ms_per_rank=ndc_fwd, params=sum(p.numel() for p in params))
 
 

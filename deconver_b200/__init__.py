@@ -11,10 +11,11 @@ from ._lib import NdcError, load as load_library
 from .deconv import NDC, Deconv, Initializer
 from .functional import DeconvUpdate, deconv_update, gconv, kernels_apply
 from .linear import Linear
+from .mlp import MLP, bias_gelu
 from .norm import InstanceNorm1d, InstanceNorm2d, InstanceNorm3d, instance_norm
 
 __all__ = [
-    "Deconv", "NDC", "Initializer", "Linear", "DeconvUpdate", "deconv_update", "gconv",
+    "Deconv", "NDC", "Initializer", "Linear", "MLP", "bias_gelu", "DeconvUpdate", "deconv_update", "gconv",
     "kernels_apply", "build_library", "load_library", "NdcError",
     "InstanceNorm1d", "InstanceNorm2d", "InstanceNorm3d", "instance_norm",
 ]

@@ -21,7 +21,7 @@ SYMBOLS = (
     "ndc_fwd", "ndc_bwd_workspace_bytes", "ndc_bwd", "ndc_bwd_static", "ndc_gconv",
     "ndc_probe_fp32_fma", "ndc_inorm_workspace_bytes", "ndc_inorm_last_error", "ndc_inorm_fwd",
     "ndc_inorm_bwd", "ndc_bias_grad_workspace_bytes", "ndc_bias_last_error", "ndc_bias_add",
-    "ndc_bias_grad",
+    "ndc_bias_grad", "ndc_bias_gelu_fwd", "ndc_bias_gelu_bwd",
 )
 
 
@@ -97,6 +97,12 @@ def load():
     lib.ndc_bias_grad.restype = ctypes.c_int
     lib.ndc_bias_grad.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp, fp,
                                   vp, ctypes.c_size_t, vp]
+    lib.ndc_bias_gelu_fwd.restype = ctypes.c_int
+    lib.ndc_bias_gelu_fwd.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp,
+                                      fp, vp, vp]
+    lib.ndc_bias_gelu_bwd.restype = ctypes.c_int
+    lib.ndc_bias_gelu_bwd.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, vp,
+                                      vp, fp, vp, fp, vp, ctypes.c_size_t, vp]
     _lib = lib
     return lib
 

@@ -1,5 +1,7 @@
 // Bias of the channels-first linear layer: y[b, c, :] += bias[c], and its gradient
-// gbias[c] = sum over samples and positions of gy[b, c, :].
+// gbias[c] = sum over samples and positions of gy[b, c, :]; and the same bias fused with the
+// exact (erf) GELU that follows the first projection of the network's MLP: a = gelu(h + bias) in
+// one pass over h, and gh = ga * gelu'(h + bias) with the bias gradient in one pass over (ga, h).
 //
 // The 1x1 projection itself is a library GEMM; what the library adds around it, a broadcast add
 // that is not vectorised and a reduction with one block per output, is slow at the small per-GPU
@@ -87,6 +89,86 @@ __global__ void bias_grad_final_kernel(const float* __restrict__ partial, int ba
     gbias[c] = s;
 }
 
+__device__ __forceinline__ float gelu_f(float u) {
+    return 0.5f * u * (1.0f + erff(u * 0.70710678118654752440f));
+}
+// d/du [u * Phi(u)] = Phi(u) + u * phi(u)
+__device__ __forceinline__ float gelu_grad_f(float u) {
+    const float cdf = 0.5f * (1.0f + erff(u * 0.70710678118654752440f));
+    const float pdf = 0.39894228040143267794f * __expf(-0.5f * u * u);
+    return fmaf(u, pdf, cdf);
+}
+
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kNT) bias_gelu_fwd_kernel(const T* __restrict__ h, T* __restrict__ out,
+                                                            long long sp, int channels, int nsplit,
+                                                            const float* __restrict__ bias) {
+    const long long slab = blockIdx.x / nsplit;
+    const int part = blockIdx.x % nsplit;
+    const T* hs = h + slab * sp;
+    T* os = out + slab * sp;
+    const float b = bias ? bias[slab % channels] : 0.0f;
+    long long begin, end;
+    part_range(sp, nsplit, part, Vec16<T>::N, begin, end);
+    constexpr int N = Vec16<T>::N;
+    if (VEC) {
+        for (long long i = begin + (long long)threadIdx.x * N; i < end; i += (long long)kNT * N) {
+            float v[N];
+            Vec16<T>::unpack(__ldg(reinterpret_cast<const typename Vec16<T>::raw*>(hs + i)), v);
+#pragma unroll
+            for (int j = 0; j < N; ++j) v[j] = gelu_f(v[j] + b);
+            *reinterpret_cast<typename Vec16<T>::raw*>(os + i) = Vec16<T>::pack(v);
+        }
+    } else {
+        for (long long i = begin + threadIdx.x; i < end; i += kNT)
+            os[i] = ndc::from_f32<T>(gelu_f(ndc::to_f32(hs[i]) + b));
+    }
+}
+
+// gh = ga * gelu'(h + bias), rounded to the storage type; partial[slab * nsplit + part] = the
+// sum of the rounded values of the part (what a separate pass over gh would add up)
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kNT) bias_gelu_bwd_kernel(const T* __restrict__ ga, const T* __restrict__ h,
+                                                            T* __restrict__ gh, long long sp, int channels,
+                                                            int nsplit, const float* __restrict__ bias,
+                                                            float* __restrict__ partial) {
+    __shared__ float scratch[2 * kNT / 32];
+    const long long slab = blockIdx.x / nsplit;
+    const int part = blockIdx.x % nsplit;
+    const T* gs = ga + slab * sp;
+    const T* hs = h + slab * sp;
+    T* os = gh + slab * sp;
+    const float b = bias ? bias[slab % channels] : 0.0f;
+    long long begin, end;
+    part_range(sp, nsplit, part, Vec16<T>::N, begin, end);
+    constexpr int N = Vec16<T>::N;
+    float s1 = 0.0f, s2 = 0.0f;
+    if (VEC) {
+        for (long long i = begin + (long long)threadIdx.x * N; i < end; i += (long long)kNT * N) {
+            float g[N], v[N];
+            Vec16<T>::unpack(__ldg(reinterpret_cast<const typename Vec16<T>::raw*>(gs + i)), g);
+            Vec16<T>::unpack(__ldg(reinterpret_cast<const typename Vec16<T>::raw*>(hs + i)), v);
+#pragma unroll
+            for (int j = 0; j < N; ++j) g[j] *= gelu_grad_f(v[j] + b);
+            const typename Vec16<T>::raw r = Vec16<T>::pack(g);
+            *reinterpret_cast<typename Vec16<T>::raw*>(os + i) = r;
+            Vec16<T>::unpack(r, g);
+#pragma unroll
+            for (int j = 0; j < N; j += 2) { s1 += g[j]; s2 += g[j + 1]; }
+        }
+    } else {
+        for (long long i = begin + threadIdx.x; i < end; i += kNT) {
+            const T r = ndc::from_f32<T>(ndc::to_f32(gs[i]) * gelu_grad_f(ndc::to_f32(hs[i]) + b));
+            os[i] = r;
+            s1 += ndc::to_f32(r);
+        }
+    }
+    if (partial) {
+        cta_sum2(s1, s2, scratch);
+        if (threadIdx.x == 0) partial[slab * nsplit + part] = s1 + s2;
+    }
+}
+
 int check(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype) {
     if (batch <= 0 || channels <= 0 || spatial <= 0)
         return bias_fail(NDC_ERR_INVALID, "bias: batch, channels and spatial size must be positive");
@@ -158,6 +240,65 @@ int ndc_bias_grad(int32_t batch, int32_t channels, int64_t spatial, int32_t dtyp
     ndc::launched(2);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return bias_fail(NDC_ERR_CUDA, "bias gradient: %s", cudaGetErrorString(e));
+    return NDC_OK;
+}
+
+int ndc_bias_gelu_fwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, const void* h,
+                      const float* bias, void* out, void* stream) {
+    if (!h || !out) return bias_fail(NDC_ERR_INVALID, "bias gelu: h and out must not be NULL");
+    int st = check(batch, channels, spatial, dtype);
+    if (st != NDC_OK) return st;
+    const long long slabs = (long long)batch * channels;
+    const int nsplit = choose_split(slabs, spatial);
+    const bool vec = spatial % (dtype == NDC_BF16 ? 8 : 4) == 0 && ((uintptr_t)h % 16) == 0 &&
+                     ((uintptr_t)out % 16) == 0;
+    const unsigned grid = (unsigned)(slabs * nsplit);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == NDC_F32) {
+        if (vec) bias_gelu_fwd_kernel<float, true><<<grid, kNT, 0, s>>>((const float*)h, (float*)out, spatial, channels, nsplit, bias);
+        else bias_gelu_fwd_kernel<float, false><<<grid, kNT, 0, s>>>((const float*)h, (float*)out, spatial, channels, nsplit, bias);
+    } else {
+        typedef __nv_bfloat16 bf16;
+        if (vec) bias_gelu_fwd_kernel<bf16, true><<<grid, kNT, 0, s>>>((const bf16*)h, (bf16*)out, spatial, channels, nsplit, bias);
+        else bias_gelu_fwd_kernel<bf16, false><<<grid, kNT, 0, s>>>((const bf16*)h, (bf16*)out, spatial, channels, nsplit, bias);
+    }
+    ndc::launched();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return bias_fail(NDC_ERR_CUDA, "bias gelu: %s", cudaGetErrorString(e));
+    return NDC_OK;
+}
+
+int ndc_bias_gelu_bwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype, const void* ga,
+                      const void* h, const float* bias, void* gh, float* gbias, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+    if (!ga || !h || !gh) return bias_fail(NDC_ERR_INVALID, "bias gelu gradient: ga, h and gh must not be NULL");
+    int st = check(batch, channels, spatial, dtype);
+    if (st != NDC_OK) return st;
+    if (gbias && (!workspace || workspace_bytes < ndc_bias_grad_workspace_bytes(batch, channels)))
+        return bias_fail(NDC_ERR_WORKSPACE, "bias gelu gradient: workspace of %zu bytes needed",
+                         ndc_bias_grad_workspace_bytes(batch, channels));
+    const long long slabs = (long long)batch * channels;
+    const int nsplit = choose_split(slabs, spatial);
+    const bool vec = spatial % (dtype == NDC_BF16 ? 8 : 4) == 0 && ((uintptr_t)ga % 16) == 0 &&
+                     ((uintptr_t)h % 16) == 0 && ((uintptr_t)gh % 16) == 0;
+    const unsigned grid = (unsigned)(slabs * nsplit);
+    cudaStream_t s = (cudaStream_t)stream;
+    float* partial = gbias ? (float*)workspace : nullptr;
+    if (dtype == NDC_F32) {
+        if (vec) bias_gelu_bwd_kernel<float, true><<<grid, kNT, 0, s>>>((const float*)ga, (const float*)h, (float*)gh, spatial, channels, nsplit, bias, partial);
+        else bias_gelu_bwd_kernel<float, false><<<grid, kNT, 0, s>>>((const float*)ga, (const float*)h, (float*)gh, spatial, channels, nsplit, bias, partial);
+    } else {
+        typedef __nv_bfloat16 bf16;
+        if (vec) bias_gelu_bwd_kernel<bf16, true><<<grid, kNT, 0, s>>>((const bf16*)ga, (const bf16*)h, (bf16*)gh, spatial, channels, nsplit, bias, partial);
+        else bias_gelu_bwd_kernel<bf16, false><<<grid, kNT, 0, s>>>((const bf16*)ga, (const bf16*)h, (bf16*)gh, spatial, channels, nsplit, bias, partial);
+    }
+    ndc::launched();
+    if (gbias) {
+        bias_grad_final_kernel<<<(channels + 127) / 128, 128, 0, s>>>(partial, batch, channels, nsplit, gbias);
+        ndc::launched();
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return bias_fail(NDC_ERR_CUDA, "bias gelu gradient: %s", cudaGetErrorString(e));
     return NDC_OK;
 }
 

@@ -896,7 +896,15 @@ __global__ void __launch_bounds__(NT, kconv2_min_blocks<NT, VK>()) kconv2_kernel
         if (qdone >= d0 && qdone < d1) finish(qdone, k_ok, kacc[DONE]);
 #pragma unroll
         for (int v = 0; v < VK; ++v) kacc[DONE][v] = pack2(0.0f, 0.0f);
-        if (WGRAD) aux_pairs(aux_next, auxs[WGRAD ? DONE : 0]);
+        if (WGRAD) {
+            // keep the conversion of the raw strips here, after the step's arithmetic: done
+            // right after the loads it would make the warp wait for them at the top of the step
+            if (sizeof(T) == 2) {
+#pragma unroll
+                for (int i = 0; i < 2 * VO; ++i) hold_raw(aux_next[i]);
+            }
+            aux_pairs(aux_next, auxs[WGRAD ? DONE : 0]);
+        }
         wait_but_newest();   // plane p+1 has landed; p+2 may still be in flight
         __syncthreads();
     };

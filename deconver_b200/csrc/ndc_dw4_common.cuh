@@ -118,6 +118,15 @@ __device__ __forceinline__ float4 to_float4(const Raw4<__nv_bfloat16>& r) {
     return make_float4(a.x, a.y, b.x, b.y);
 }
 
+// An opaque use of a raw strip: what is computed from it afterwards cannot be scheduled before
+// this point.
+__device__ __forceinline__ void hold_raw(Raw4<float>& r) {
+    asm volatile("" : "+f"(r.v.x), "+f"(r.v.y), "+f"(r.v.z), "+f"(r.v.w));
+}
+__device__ __forceinline__ void hold_raw(Raw4<__nv_bfloat16>& r) {
+    asm volatile("" : "+r"(r.v.x), "+r"(r.v.y));
+}
+
 template <typename T, bool VEC>
 __device__ __forceinline__ Raw4<T> load4_raw(const T* p, int n);
 template <>

@@ -215,6 +215,23 @@ int ndc_bias_grad(int32_t batch, int32_t channels, int64_t spatial, int32_t dtyp
                   float *gbias, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * The same bias fused with the exact (erf) GELU between the two projections of the network's
+ * MLP (`MLP`, deconver/layers/mlp.py:53-59: Linear, nn.GELU(), Dropout, Linear, Dropout), for
+ * the bias-less product h of the first projection:
+ *     ndc_bias_gelu_fwd   out = gelu(h + bias[c])                      one pass over h
+ *     ndc_bias_gelu_bwd   gh = ga * gelu'(h + bias[c]);  gbias[c] = sum_{b, p} gh[b, c, p]
+ * bias may be NULL (plain GELU); gbias may be NULL (then no workspace is needed), else it is
+ * float32, overwritten, summed in a fixed order and the call needs
+ * ndc_bias_grad_workspace_bytes(batch, channels) bytes of device scratch.  out / gh may not
+ * alias h.  Errors as above.
+ */
+int ndc_bias_gelu_fwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype,
+                      const void *h, const float *bias, void *out, void *stream);
+int ndc_bias_gelu_bwd(int32_t batch, int32_t channels, int64_t spatial, int32_t dtype,
+                      const void *ga, const void *h, const float *bias, void *gh, float *gbias,
+                      void *workspace, size_t workspace_bytes, void *stream);
+
+/*
  * Measurement aid; no counterpart in the reference project.  Launches one kernel of
  * register-only fused multiply-add chains (4 blocks of 256 threads per multiprocessor, 8
  * independent chains per thread, iters x 64 instructions per thread) on `stream`: plain

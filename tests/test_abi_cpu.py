@@ -166,3 +166,10 @@ def test_bias_entry_points_validate_without_a_gpu(lib):
     assert lib.ndc_bias_add(2, 64, 4096, 0, None, None, None) == 1
     assert b"NULL" in lib.ndc_bias_last_error()
     assert lib.ndc_bias_grad(2, 64, 4096, 0, None, None, None, 0, None) == 1
+    assert lib.ndc_bias_gelu_fwd(2, 64, 4096, 0, None, None, None, None) == 1
+    assert b"NULL" in lib.ndc_bias_last_error()
+    assert lib.ndc_bias_gelu_bwd(2, 64, 4096, 0, None, None, None, None, None, None, 0, None) == 1
+    assert lib.ndc_bias_gelu_fwd(0, 64, 4096, 0, 16, None, 16, None) == 1
+    assert b"positive" in lib.ndc_bias_last_error()
+    assert lib.ndc_bias_gelu_fwd(2, 64, 4096, 7, 16, None, 16, None) == 1
+    assert b"dtype" in lib.ndc_bias_last_error()

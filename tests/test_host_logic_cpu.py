@@ -136,3 +136,10 @@ def test_instance_norm_module_host_logic():
         dcb.InstanceNorm1d(4)(torch.randn(2, 4, 10))          # there is no CPU path
     with pytest.raises(ValueError):
         dcb.InstanceNorm2d(4)(torch.randn(2, 4, 10))
+
+
+def test_mlp_cpu_tensors_run_the_plain_sequence():
+    m = dcb.MLP(4, out_channels=6, ratio=2, dropout=(0.0, 0.0))
+    x = torch.randn(2, 4, 5, 5)
+    ref = m.block(x)
+    assert torch.equal(m(x), ref) and ref.shape == (2, 6, 5, 5)

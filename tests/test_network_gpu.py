@@ -46,13 +46,14 @@ def reference():
 
 
 def _network(reference, layer_cls, dev, norm=None):
-    """`norm` given: the network also gets this library's InstanceNorm3d and Linear."""
+    """`norm` given: the network also gets this library's InstanceNorm3d, Linear and MLP."""
     dc, module, _ = reference
     import deconver.layers.mlp as mlp_module
-    original, linear = module.Deconv, module.Linear
+    original, linear, mlp = module.Deconv, module.Linear, module.MLP
     module.Deconv = layer_cls
     if norm is not None:
         module.Linear = mlp_module.Linear = dcb.Linear
+        module.MLP = dcb.MLP
     try:
         torch.manual_seed(0)
         kwargs = dict(NETWORK, norm=norm) if norm is not None else NETWORK
@@ -60,6 +61,7 @@ def _network(reference, layer_cls, dev, norm=None):
     finally:
         module.Deconv = original
         module.Linear = mlp_module.Linear = linear
+        module.MLP = mlp
 
 
 def _errors(a, b):
@@ -80,6 +82,7 @@ def test_network_on_this_layer_is_as_close_to_float64_as_the_original(reference,
     assert any(isinstance(m, dcb.InstanceNorm3d) for m in new.modules()) == own_norm
     mixers = [m for m in new.modules() if type(m).__name__ == "DeconvMixer"]
     assert mixers and all((type(m.out_proj) is dcb.Linear) == own_norm for m in mixers)
+    assert any(isinstance(m, dcb.MLP) for m in new.modules()) == own_norm
     assert any(isinstance(m, dcb.Deconv) for m in new.modules())
     assert not any(isinstance(m, ReferenceDeconv) for m in new.modules())
     assert list(old.state_dict()) == list(new.state_dict())
