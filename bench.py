@@ -308,7 +308,7 @@ def sub_records(args, world, rank):
         rec["ms_per_step_without_cuda_graph"] = eager["ms_per_step"]
         rec["workload"] = ("full 3D Deconver training step (fwd+bwd+SGD), bf16, global batch 16 "
                            "of 2x64^3 split over the ranks (strong scaling); the reference's "
-                           "network with this library's NDC layer and InstanceNorm3d")
+                           "network with this library's NDC layer, InstanceNorm3d, Linear and MLP")
         out["train_step"] = rec
     except Exception as exc:
         out["train_step"] = {"unavailable": f"{type(exc).__name__}: {exc}"}
