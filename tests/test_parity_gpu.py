@@ -608,3 +608,54 @@ def test_tiled_kernels_match_generic_kernels_on_random_geometries(dev):
         for name, a, r in zip(("out", "gx", "gz", "gh", "gb"), res[1], res[0]):
             err = max_norm_error(a.cpu().numpy(), r.cpu().numpy())
             assert err < F32_TOL, f"{name} error {err:.3e} for B={B} C={C} k={ks} S={spatial} relu={relu}"
+
+
+def test_tiled_kernels_match_generic_kernels_on_a_sweep_of_kernel_classes(dev):
+    """Second seeded sweep, aimed at the launch classes of the 3x3x3 kernels: small cubes with
+    many channels (the narrow CTAs), rows of 60..256 voxels (the wide packed-K CTA), deep volumes
+    with few and with many slabs (depth chunks and none), float32 and bfloat16 storage."""
+    rng = np.random.default_rng(7)
+    cases = []
+    for _ in range(80):
+        r = rng.random()
+        if r < 0.25:
+            n = int(rng.choice([4, 8, 12, 16, 20, 24, 32]))
+            spatial = (n + int(rng.integers(0, 3)), n, n + int(rng.integers(0, 4)))
+            B, C = int(rng.integers(1, 4)), int(rng.integers(1, 40))
+        elif r < 0.5:
+            spatial = (int(rng.integers(1, 20)), int(rng.integers(1, 30)), int(rng.integers(60, 257)))
+            B, C = int(rng.integers(1, 3)), int(rng.integers(1, 4))
+        elif r < 0.75:
+            spatial = (int(rng.integers(30, 100)), int(rng.integers(4, 40)), int(rng.integers(4, 70)))
+            B, C = int(rng.integers(1, 3)), int(rng.choice([1, 2, 8, 32]))
+        else:
+            spatial = (int(rng.integers(1, 45)), int(rng.integers(1, 70)), int(rng.integers(1, 75)))
+            B, C = int(rng.integers(1, 3)), int(rng.integers(1, 5))
+        if B * C * 4 * np.prod(spatial) > 6e7:
+            C = max(1, int(6e7 / (B * 4 * np.prod(spatial))))
+        cases.append((B, C, spatial, bool(rng.random() < 0.7), bool(rng.random() < 0.3)))
+    ks = (3, 3, 3)
+    for i, (B, C, spatial, relu, bf16) in enumerate(cases):
+        dt = torch.bfloat16 if bf16 else torch.float32
+        gen = torch.Generator(device=dev).manual_seed(i)
+        x = torch.rand(B, C, *spatial, device=dev, generator=gen).to(dt)
+        z = (torch.randn(B, 4 * C, *spatial, device=dev, generator=gen) * 0.5 + 0.3).to(dt)
+        if not relu:
+            z = z.abs()
+        h = torch.rand(C, 4, *ks, device=dev, generator=gen) / 27.0
+        bias = torch.randn(4 * C, device=dev, generator=gen) * 0.1 if relu else None
+        gout = torch.randn(B, 4 * C, *spatial, device=dev, generator=gen).to(dt)
+        cfg = dict(groups=C, m=1, sc=4, eps=1e-16, relu_input=relu)
+        res = []
+        for generic in (True, False):
+            t = [v.clone().requires_grad_(True) for v in (x, z, h)]
+            b = None if bias is None else bias.clone().requires_grad_(True)
+            with Fn.force_generic(generic):
+                out = dcb.deconv_update(t[0], t[1], t[2], b, **cfg)
+                out.backward(gout)
+            res.append([out.detach()] + [v.grad for v in t] + ([] if b is None else [b.grad]))
+        torch.cuda.synchronize()
+        tol = BF16_TOL if bf16 else F32_TOL
+        for name, a, r in zip(("out", "gx", "gz", "gh", "gb"), res[1], res[0]):
+            err = max_norm_error(a.float().cpu().numpy(), r.float().cpu().numpy())
+            assert err < tol, f"{name} error {err:.3e} for B={B} C={C} S={spatial} relu={relu} bf16={bf16}"
