@@ -143,3 +143,29 @@ def test_mlp_cpu_tensors_run_the_plain_sequence():
     x = torch.randn(2, 4, 5, 5)
     ref = m.block(x)
     assert torch.equal(m(x), ref) and ref.shape == (2, 6, 5, 5)
+
+
+def test_linear_and_mlp_keep_the_reference_state_dict_layout():
+    """Against an installation of the reference where there is one (`baseline/_ref`): same
+    state-dict keys and shapes for `Linear` (`layers/linear.py`) and `MLP` (`layers/mlp.py`),
+    and weights move both ways."""
+    import os
+    import sys
+    ref_root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "deconver")):
+        pytest.skip("no reference installation under baseline/_ref")
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    from deconver.layers.linear import Linear as RefLinear
+    from deconver.layers.mlp import MLP as RefMLP
+    pairs = [(RefLinear(6, 10), dcb.Linear(6, 10)), (RefLinear(6, 10, bias=False), dcb.Linear(6, 10, bias=False)),
+             (RefMLP(8, ratio=4), dcb.MLP(8, ratio=4)), (RefMLP(8, 5, hidden_channels=12), dcb.MLP(8, 5, hidden_channels=12))]
+    x = {6: torch.randn(2, 6, 4, 5), 8: torch.randn(2, 8, 3, 3, 3)}
+    for ref, mine in pairs:
+        ref_sd, my_sd = ref.state_dict(), mine.state_dict()
+        assert list(ref_sd) == list(my_sd)
+        assert [tuple(v.shape) for v in ref_sd.values()] == [tuple(v.shape) for v in my_sd.values()]
+        mine.load_state_dict(ref_sd, strict=True)
+        ref.load_state_dict(mine.state_dict(), strict=True)
+        inp = x[next(iter(ref_sd.values())).shape[1]]
+        assert torch.allclose(ref(inp), mine(inp), atol=1e-6)     # CPU tensors: the plain sequence
