@@ -43,6 +43,16 @@ def force_generic(enabled: bool = True):
         _flags = old
 
 
+_NO_SPAN = contextlib.nullcontext()
+
+
+def _on_device(device):
+    """Device guard for the C-ABI calls; free when `device` is already the current one."""
+    if device.index is None or device.index == torch.cuda.current_device():
+        return _NO_SPAN
+    return torch.cuda.device(device)
+
+
 class _Timing:
     """Optional CUDA-event timing of the C-ABI calls, on the stream they are issued on.
 
@@ -58,11 +68,11 @@ class _Timing:
         self._events = {"ndc_fwd": [], "ndc_bwd": []}
         self.enabled = True
 
-    @contextlib.contextmanager
     def span(self, name: str):
-        if not self.enabled:
-            yield
-            return
+        return self._span(name) if self.enabled else _NO_SPAN
+
+    @contextlib.contextmanager
+    def _span(self, name: str):
         start = torch.cuda.Event(enable_timing=True)
         stop = torch.cuda.Event(enable_timing=True)
         start.record()
@@ -81,6 +91,9 @@ class _Timing:
 timing = _Timing()
 
 
+_kernels_apply_cache = {}
+
+
 def kernels_apply(x: Tensor, m: int, sc: int, kernel_size: Sequence[int]) -> bool:
     """Whether the CUDA kernels cover this input and filter geometry.
 
@@ -90,12 +103,20 @@ def kernels_apply(x: Tensor, m: int, sc: int, kernel_size: Sequence[int]) -> boo
         return False
     if len(kernel_size) != x.dim() - 2 or any(k % 2 == 0 for k in kernel_size):
         return False
-    desc = _lib.make_desc(max(x.shape[0], 1), 1, m, sc, [max(v, 1) for v in x.shape[2:]],
-                          kernel_size, 0.0, True, _DTYPES[x.dtype])
-    return _lib.load().ndc_query(desc, None) == _lib.NDC_OK
+    # the answer depends on the geometry only: asked once per geometry, not once per call
+    key = (x.dtype, x.shape[0], tuple(x.shape[2:]), m, sc, tuple(kernel_size))
+    known = _kernels_apply_cache.get(key)
+    if known is None:
+        desc = _lib.make_desc(max(x.shape[0], 1), 1, m, sc, [max(v, 1) for v in x.shape[2:]],
+                              kernel_size, 0.0, True, _DTYPES[x.dtype])
+        known = _lib.load().ndc_query(desc, None) == _lib.NDC_OK
+        if len(_kernels_apply_cache) < 4096:
+            _kernels_apply_cache[key] = known
+    return known
 
 
 _warned_generic = set()
+_checked_tiled = set()     # geometries already known to run on the tiled kernels
 
 
 def _warn_if_generic(desc, flags: int) -> None:
@@ -106,8 +127,14 @@ def _warn_if_generic(desc, flags: int) -> None:
     key = (desc.kD, desc.kH, desc.kW, desc.W > 256, desc.dtype)
     if key in _warned_generic:
         return
+    seen = (desc.batch, desc.groups, desc.D, desc.H, desc.W, desc.kD, desc.kH, desc.kW, desc.dtype)
+    if seen in _checked_tiled:
+        return
     path = ctypes.c_int32(-1)
-    if _lib.load().ndc_query(desc, ctypes.byref(path)) == _lib.NDC_OK and path.value == _lib.PATH_GENERIC:
+    status = _lib.load().ndc_query(desc, ctypes.byref(path))
+    if status == _lib.NDC_OK and path.value != _lib.PATH_GENERIC and len(_checked_tiled) < 4096:
+        _checked_tiled.add(seen)
+    if status == _lib.NDC_OK and path.value == _lib.PATH_GENERIC:
         _warned_generic.add(key)
         warnings.warn(
             f"deconver_b200: depthwise ratio-4 update with kernel ({desc.kD},{desc.kH},{desc.kW}) on "
@@ -134,7 +161,12 @@ def _ptr(t: Optional[Tensor]):
 
 def _f32(t: Optional[Tensor]) -> Optional[Tensor]:
     """Filter and bias are handed to the kernels in float32 whatever the model's dtype."""
-    return None if t is None else t.detach().to(torch.float32).contiguous()
+    if t is None:
+        return None
+    t = t.detach()
+    if t.dtype != torch.float32:
+        t = t.to(torch.float32)
+    return t if t.is_contiguous() else t.contiguous()
 
 
 def _desc(x: Tensor, groups: int, m: int, sc: int, ks, eps: float, relu_input: bool,
@@ -180,7 +212,7 @@ class DeconvUpdate(torch.autograd.Function):
         out = torch.empty_like(z)
         t1 = torch.empty_like(x)
         if x.numel() and z.numel():
-            with torch.cuda.device(x.device):
+            with _on_device(x.device):
                 stream = torch.cuda.current_stream().cuda_stream
                 with timing.span("ndc_fwd"):
                     _lib.check(_lib.load().ndc_fwd(desc, _ptr(x), _ptr(z), _ptr(hf), _ptr(bf),
@@ -217,7 +249,7 @@ class DeconvUpdate(torch.autograd.Function):
         gb = torch.empty(bias.shape, device=x.device, dtype=torch.float32) if need_b else None
         if x.numel() and z.numel():
             lib = _lib.load()
-            with torch.cuda.device(x.device):
+            with _on_device(x.device):
                 nbytes = lib.ndc_bwd_workspace_bytes(desc)
                 ws = torch.empty(max(nbytes, 1), device=x.device, dtype=torch.uint8)
                 stream = torch.cuda.current_stream().cuda_stream
