@@ -199,7 +199,7 @@ inline bool plan_ring(int D, int H, int W, long long BC, int ntensors, int nt, i
         t.nth = best_nth;
     }
     t.TH = (H + t.nth - 1) / t.nth;
-    plan_depth(KD, D, BC * t.nth, 6, t, ctas_per_sm);
+    plan_depth(KD, D, BC * t.nth, 4, t, ctas_per_sm);
     smem_bytes = bytes(t.TH);
     return true;
 }
