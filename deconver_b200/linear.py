@@ -68,17 +68,18 @@ def _weight_grad(gy: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
     sample).  At the small per-GPU batches of a batch-sharded training step the library's
     convolution backward takes 3-4x the time the two reads need (0.31 ms against 0.09 ms for
     bfloat16 tensors of 2 x 256 x 64^3 and 2 x 64 x 64^3).  Here the positions of each sample
-    are cut into S slices and ONE strided batched GEMM (library) multiplies all slices, with
+    are cut into S slices (up to 32, of at least 2048 positions: enough tiles per launch to
+    fill the GPU) and ONE strided batched GEMM (library) multiplies all slices, with
     float32 partial products (the samples accumulate into the same S partial products, which are
     then added in a fixed order); no operand is copied: the slices are views of the tensors as
     they lie.  Batches above 4, float32 and CPU tensors keep
     the library's own weight gradient, which is the faster one there (measured on the 3-D
-    network's training step: 28.7 against 29.6 ms at batch 4, 56.7 against 52.7 ms at batch 8).
+    network's training step: 28.1 against 29.6 ms at batch 4, level at 52.7 ms at batch 8).
     """
     B, Co, N = gy.shape
     Ci = x.shape[1]
     S = 1
-    while S * 2 * B <= 32 and N % (S * 2 * 8) == 0 and N // (S * 2) >= 2048:
+    while S * 2 <= 32 and N % (S * 2 * 8) == 0 and N // (S * 2) >= 2048:
         S *= 2
     if gy.dtype != torch.bfloat16 or not gy.is_cuda or B > 4 or S == 1:
         return torch.nn.grad.conv1d_weight(x, (Co, Ci, 1), gy)[:, :, 0]
