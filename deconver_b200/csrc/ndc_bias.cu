@@ -1,6 +1,6 @@
 // Bias of the channels-first linear layer: y[b, c, :] += bias[c], and its gradient
 // gbias[c] = sum over samples and positions of gy[b, c, :]; and the same bias fused with the
-// exact (erf) GELU that follows the first projection of the network's MLP: a = gelu(h + bias) in
+// erf-form GELU that follows the first projection of the network's MLP: a = gelu(h + bias) in
 // one pass over h, and gh = ga * gelu'(h + bias) with the bias gradient in one pass over (ga, h).
 //
 // The 1x1 projection itself is a library GEMM; what the library adds around it, a broadcast add
