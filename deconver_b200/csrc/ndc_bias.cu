@@ -117,6 +117,72 @@ __device__ __forceinline__ float gelu_grad_f(float u) {
     return fmaf(u, 0.39894228040143267794f * e, cdf);
 }
 
+// The same arithmetic on two elements at a time: the adds, multiplies and multiply-adds are
+// two-lane `*.rn.f32x2` instructions (each lane rounds like the scalar form), the reciprocal and
+// the exponential stay per lane.  About 12 instructions per element instead of 20: the
+// vectorised GELU passes were bound by instruction issue, not by memory.
+typedef unsigned long long f2;
+__device__ __forceinline__ f2 f2_pack(float lo, float hi) {
+    f2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(f2 p, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+}
+__device__ __forceinline__ f2 f2_fma(f2 a, f2 b, f2 c) {
+    f2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f2 f2_mul(f2 a, f2 b) {
+    f2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f2 f2_add(f2 a, f2 b) {
+    f2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f2 f2_dup(float v) { return f2_pack(v, v); }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// cdf = Phi(u) for both lanes; e = exp(-u^2 / 2) for both lanes
+__device__ __forceinline__ f2 gelu_cdf2(f2 u, f2& e) {
+    float u0, u1;
+    f2_unpack(u, u0, u1);
+    const f2 au = f2_pack(fabsf(u0), fabsf(u1));
+    // x = u / sqrt(2): t = 1 / (1 + p |x|), e = exp(-x^2) = exp2(-u^2 * log2(e) / 2)
+    float d0, d1;
+    f2_unpack(f2_fma(f2_dup(0.3275911f * 0.70710678118654752440f), au, f2_dup(1.0f)), d0, d1);
+    const f2 t = f2_pack(__frcp_rn(d0), __frcp_rn(d1));
+    f2 p = f2_fma(f2_dup(1.061405429f), t, f2_dup(-1.453152027f));
+    p = f2_fma(p, t, f2_dup(1.421413741f));
+    p = f2_fma(p, t, f2_dup(-0.284496736f));
+    p = f2_fma(p, t, f2_dup(0.254829592f));
+    float s0, s1;
+    f2_unpack(f2_mul(f2_mul(u, u), f2_dup(-0.72134752044448170368f)), s0, s1);
+    e = f2_pack(ex2_approx(s0), ex2_approx(s1));
+    // 1 - erf(|x|) = p t e;  Phi = 0.5 + copysign(0.5 - 0.5 p t e, u)
+    float h0, h1;
+    f2_unpack(f2_fma(f2_mul(p, t), f2_mul(e, f2_dup(-0.5f)), f2_dup(0.5f)), h0, h1);
+    return f2_add(f2_pack(copysignf(h0, u0), copysignf(h1, u1)), f2_dup(0.5f));
+}
+__device__ __forceinline__ f2 gelu2(f2 u) {
+    f2 e;
+    return f2_mul(u, gelu_cdf2(u, e));
+}
+__device__ __forceinline__ f2 gelu_grad2(f2 u) {
+    f2 e;
+    const f2 cdf = gelu_cdf2(u, e);
+    return f2_fma(u, f2_mul(e, f2_dup(0.39894228040143267794f)), cdf);
+}
+
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kNT) bias_gelu_fwd_kernel(const T* __restrict__ h, T* __restrict__ out,
                                                             long long sp, int channels, int nsplit,
@@ -134,6 +200,7 @@ __global__ void __launch_bounds__(kNT) bias_gelu_fwd_kernel(const T* __restrict_
         // arithmetic of one vector is long enough to leave the memory pipe idle otherwise
         typedef typename Vec16<T>::raw Raw;
         const long long step = (long long)kNT * N;
+        const f2 b2 = f2_dup(b);
         long long i = begin + (long long)threadIdx.x * N;
         for (; i + (kGeluUnroll - 1) * step < end; i += kGeluUnroll * step) {
             Raw r[kGeluUnroll];
@@ -144,7 +211,8 @@ __global__ void __launch_bounds__(kNT) bias_gelu_fwd_kernel(const T* __restrict_
                 float v[N];
                 Vec16<T>::unpack(r[u], v);
 #pragma unroll
-                for (int j = 0; j < N; ++j) v[j] = gelu_f(v[j] + b);
+                for (int j = 0; j < N; j += 2)
+                    f2_unpack(gelu2(f2_add(f2_pack(v[j], v[j + 1]), b2)), v[j], v[j + 1]);
                 *reinterpret_cast<Raw*>(os + i + u * step) = Vec16<T>::pack(v);
             }
         }
@@ -152,7 +220,8 @@ __global__ void __launch_bounds__(kNT) bias_gelu_fwd_kernel(const T* __restrict_
             float v[N];
             Vec16<T>::unpack(__ldg(reinterpret_cast<const Raw*>(hs + i)), v);
 #pragma unroll
-            for (int j = 0; j < N; ++j) v[j] = gelu_f(v[j] + b);
+            for (int j = 0; j < N; j += 2)
+                f2_unpack(gelu2(f2_add(f2_pack(v[j], v[j + 1]), b2)), v[j], v[j + 1]);
             *reinterpret_cast<Raw*>(os + i) = Vec16<T>::pack(v);
         }
     } else {
@@ -182,12 +251,15 @@ __global__ void __launch_bounds__(kNT) bias_gelu_bwd_kernel(const T* __restrict_
     if (VEC) {
         typedef typename Vec16<T>::raw Raw;
         const long long step = (long long)kNT * N;
+        const f2 b2 = f2_dup(b);
         auto one = [&](const Raw& rg, const Raw& rh, long long at) {
             float g[N], v[N];
             Vec16<T>::unpack(rg, g);
             Vec16<T>::unpack(rh, v);
 #pragma unroll
-            for (int j = 0; j < N; ++j) g[j] *= gelu_grad_f(v[j] + b);
+            for (int j = 0; j < N; j += 2)
+                f2_unpack(f2_mul(f2_pack(g[j], g[j + 1]), gelu_grad2(f2_add(f2_pack(v[j], v[j + 1]), b2))),
+                          g[j], g[j + 1]);
             const Raw r = Vec16<T>::pack(g);
             *reinterpret_cast<Raw*>(os + at) = r;
             Vec16<T>::unpack(r, g);
